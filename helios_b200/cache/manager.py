@@ -79,7 +79,8 @@ def pool_sizes_for_bytes(plan: ModelPlan, page_size: int, dtype_bytes: int, kv_c
         if spec.window is not None:
             sizes[g] = share
             if max_slots is not None and largest_portion is not None:
-                per_request = -(-(spec.window + largest_portion) // page_size) + 2
+                per_request = -(-(spec.window + largest_portion) // page_size) + 2 \
+                    + -(-spec.keep_first // page_size)
                 sizes[g] = max(8, min(share, max_slots * per_request))
             left -= sizes[g] * per_page[g]
     full_bytes = sum(per_page[g] for g in range(len(specs)) if sizes[g] is None)
@@ -100,7 +101,8 @@ class KVCacheManager(CacheLayout):
             num_pages = [num_pages] * len(specs)
         if len(num_pages) != len(specs):
             raise ValueError(f"{len(num_pages)} pool sizes for {len(specs)} cache groups")
-        super().__init__([GroupLayout(s.window, n) for s, n in zip(specs, num_pages)],
+        super().__init__([GroupLayout(s.window, n, s.keep_first if s.window is not None else 0)
+                          for s, n in zip(specs, num_pages)],
                          page_size, max_slots, watermark)
         self.plan = plan
         self.specs = specs

@@ -8,7 +8,8 @@ A model's cache ids are put into groups by what they store per token (KV heads,
 head size, all keys or a window).  Every group has a pool of pages of its own
 and every request a block table per group.  Pages are taken when tokens are
 about to be written, given back when the request ends, and, in a group with a
-window, as soon as the window has passed them; a page that was given back is
+window, as soon as the window has passed them (but for the pages that hold the
+first tokens, where the group keeps those); a page that was given back is
 handed out again (first freed, first reused).
 """
 from __future__ import annotations
@@ -87,6 +88,7 @@ class GroupLayout:
     """What the bookkeeping has to know of a group."""
     window: Optional[int]      # None: all keys; W: the last W keys
     num_pages: int
+    keep_first: int = 0        # with a window: the request's first tokens stay as well
 
 
 @dataclass
@@ -94,7 +96,8 @@ class RequestPages:
     slot: int
     length: int = 0                                  # tokens written and committed
     tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> id, -1 once given back
-    first_held: List[int] = field(default_factory=list)     # per group: first logical page still held
+    # per group: first logical page still held behind the kept first pages (0: none given back yet)
+    first_held: List[int] = field(default_factory=list)
     version: int = 0                                 # counts the changes of ``tables``
     arrays: dict = field(default_factory=dict)       # group -> (version, tables[group] as int32 array)
 
@@ -122,6 +125,10 @@ class CacheLayout:
     def pages_for_tokens(self, n_tokens: int) -> int:
         return -(-n_tokens // self.page_size)
 
+    def kept_pages(self, group: int) -> int:
+        """Pages at the start of a request that a window group never gives back."""
+        return self.pages_for_tokens(self.groups[group].keep_first)
+
     def peak_pages(self, group: int, total_tokens: int, largest_portion: int) -> int:
         """Most pages of ``group`` a request of ``total_tokens`` holds at any time when it
         is fed in portions of at most ``largest_portion`` tokens."""
@@ -129,7 +136,8 @@ class CacheLayout:
         if w is None:
             return self.pages_for_tokens(total_tokens)
         span = min(total_tokens, w + max(1, largest_portion))
-        return min(self.pages_for_tokens(total_tokens), self.pages_for_tokens(span) + 1)
+        return min(self.pages_for_tokens(total_tokens),
+                   self.pages_for_tokens(span) + 1 + self.kept_pages(group))
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id: Hashable) -> bool:
@@ -220,7 +228,8 @@ class CacheLayout:
     def pages_held(self, request_id: Hashable) -> List[int]:
         """Pages per group the request holds now (the ones a window has passed are gone)."""
         req = self.requests[request_id]
-        return [len(t) - first for t, first in zip(req.tables, req.first_held)]
+        return [len(t) - max(0, first - self.kept_pages(g))
+                for g, (t, first) in enumerate(zip(req.tables, req.first_held))]
 
     def tokens_that_fit(self, request_id: Hashable, keep_free: Optional[Sequence[int]] = None) -> int:
         """How many more tokens the request can take pages for right now, leaving
@@ -278,12 +287,13 @@ class CacheLayout:
             first_needed = max(0, req.length - group.window + 1) // self.page_size
             table = req.tables[g]
             dead = []
-            while req.first_held[g] < min(first_needed, len(table)):
-                j = req.first_held[g]
+            j = max(req.first_held[g], self.kept_pages(g))       # the kept first pages are passed over
+            while j < min(first_needed, len(table)):
                 dead.append(table[j])
                 table[j] = -1
-                req.first_held[g] += 1
+                j += 1
             if dead:
+                req.first_held[g] = j
                 self.pools[g].give_back(dead, request_id)
                 req.version += 1
 
@@ -312,11 +322,12 @@ class CacheLayout:
                 if len(table) < self.pages_for_tokens(req.length):
                     raise CacheInvariantError(f"request {rid!r} has tokens without pages")
                 for j, p in enumerate(table):
+                    kept = self.kept_pages(g)
                     if p < 0:
-                        if self.groups[g].window is None or j >= req.first_held[g]:
+                        if self.groups[g].window is None or j >= req.first_held[g] or j < kept:
                             raise CacheInvariantError(f"request {rid!r} lost page {j} of group {g}")
                         continue
-                    if j < req.first_held[g]:
+                    if kept <= j < req.first_held[g]:
                         raise CacheInvariantError(f"request {rid!r} holds a page behind its window")
                     if p in seen:
                         raise CacheInvariantError(f"page {p} of group {g} is held by {seen[p]!r} and {rid!r}")

@@ -6,9 +6,12 @@
 // (python/helios/exec/paged_attn.py:264-295, 368-408; GQA mapping :248-261).
 //
 // Options, each off by default: values of another size than the keys (`vd`); a bias on the
-// score that grows with the distance, score - slopes[h] * (p - j); a sink in the softmax, a
-// key of score 0 without a value, so that the weights are exp(s_j) / (1 + sum exp(s_j)); a
-// gate per (token, head), the head's output times sigmoid(gate[t, h]).
+// score that grows with the distance, score - slopes[h] * (p - j); a bias looked up by the
+// distance, score + bias_table[min(p - j, bias_rows - 1), h]; first tokens that a window
+// keeps (`keep_first`: j visible if j <= p and (p - j < window or j < keep_first)); a sink in
+// the softmax, a key without a value whose score is 0 or sink_values[h], so that the weights
+// are exp(s_j) / (exp(sink) + sum exp(s_j)); a gate per (token, head), the head's output times
+// sigmoid(gate[t, h]), or per output value (`gate_wide`: gate[t, h * vd + d]).
 //
 // Scores, softmax and the weighted sum are float32.  The keys are walked in
 // runs of 32 from `lo`, so the order of every sum depends on the token's
@@ -26,7 +29,8 @@ __global__ void attention_generic_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, int n_rows, int nh, int nkv, int hd, int vd, int page_size,
     int window, float scale, const float* __restrict__ slopes, int sink,
-    const T* __restrict__ gate, int gate_stride) {
+    const T* __restrict__ gate, int gate_stride, const float* __restrict__ bias_table, int bias_rows,
+    const float* __restrict__ sink_values, int keep_first, int gate_wide) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float q_smem[ATTN_WARPS][ATTN_MAX_HD];
@@ -51,51 +55,63 @@ __global__ void attention_generic_kernel(
   float m = -INFINITY, l = 0.f;
   const float slope = slopes ? slopes[h] : 0.f;
 
-  for (int base = lo; base <= pos; base += 32) {
-    const int key = base + lane;
-    const bool valid = key <= pos;
-    int page = 0;
-    float score = -INFINITY;
-    if (valid) {
-      page = table[key / page_size];
-      const T* kr = k_pages + (((size_t)page * nkv + kvh) * page_size + key % page_size) * hd;
-      float dot = 0.f;
-      for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
-      score = dot * scale - slope * (float)(pos - key);
-    }
-    const float m_new = fmaxf(m, warp_max(score));
-    const float p = valid ? expf(score - m_new) : 0.f;
-    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    l = l * corr + warp_sum(p);
-    m = m_new;
+  // two stretches of keys: the first tokens a window keeps (those it has passed), then the
+  // window itself; each in runs of 32 from its own first key
+  for (int stretch = 0; stretch < 2; ++stretch) {
+    const int first = stretch == 0 ? 0 : lo;
+    const int last = stretch == 0 ? min(keep_first, lo) - 1 : pos;
+    for (int base = first; base <= last; base += 32) {
+      const int key = base + lane;
+      const bool valid = key <= last;
+      int page = 0;
+      float score = -INFINITY;
+      if (valid) {
+        page = table[key / page_size];
+        const T* kr = k_pages + (((size_t)page * nkv + kvh) * page_size + key % page_size) * hd;
+        float dot = 0.f;
+        for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
+        score = dot * scale - slope * (float)(pos - key);
+        if (bias_table) score += bias_table[(size_t)min(pos - key, bias_rows - 1) * nh + h];
+      }
+      const float m_new = fmaxf(m, warp_max(score));
+      const float p = valid ? expf(score - m_new) : 0.f;
+      const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      l = l * corr + warp_sum(p);
+      m = m_new;
 #pragma unroll
-    for (int i = 0; i < ND; ++i) acc[i] *= corr;
-    const int n_valid = min(32, pos - base + 1);
-    for (int j = 0; j < n_valid; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const int pagej = __shfl_sync(0xffffffffu, page, j);
-      const T* vr = v_pages + (((size_t)pagej * nkv + kvh) * page_size + (base + j) % page_size) * vd;
+      for (int i = 0; i < ND; ++i) acc[i] *= corr;
+      const int n_valid = min(32, last - base + 1);
+      for (int j = 0; j < n_valid; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const int pagej = __shfl_sync(0xffffffffu, page, j);
+        const T* vr = v_pages + (((size_t)pagej * nkv + kvh) * page_size + (base + j) % page_size) * vd;
 #pragma unroll
-      for (int i = 0; i < ND; ++i) {
-        const int d = lane + 32 * i;
-        if (d < vd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+        for (int i = 0; i < ND; ++i) {
+          const int d = lane + 32 * i;
+          if (d < vd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+        }
       }
     }
   }
-  if (sink) {                       // the key of score 0: it adds exp(0 - m) to the sum only
-    const float m_new = fmaxf(m, 0.f);
+  if (sink) {                       // a key without a value: it adds exp(s - m) to the sum only (s = 0 unless given)
+    const float sv = sink_values ? sink_values[h] : 0.f;
+    const float m_new = fmaxf(m, sv);
     const float corr = expf(m - m_new);
-    l = l * corr + expf(-m_new);
+    l = l * corr + expf(sv - m_new);
 #pragma unroll
     for (int i = 0; i < ND; ++i) acc[i] *= corr;
   }
   float inv = 1.f / l;
-  if (gate) inv /= 1.f + expf(-to_float(gate[(size_t)t * gate_stride + h]));
+  if (gate && !gate_wide) inv /= 1.f + expf(-to_float(gate[(size_t)t * gate_stride + h]));
   T* orow = out + (size_t)t * nh * vd + (size_t)h * vd;
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
-    if (d < vd) orow[d] = from_float<T>(acc[i] * inv);
+    if (d < vd) {
+      float y = acc[i] * inv;
+      if (gate && gate_wide) y /= 1.f + expf(-to_float(gate[(size_t)t * gate_stride + (size_t)h * vd + d]));
+      orow[d] = from_float<T>(y);
+    }
   }
 }
 
@@ -104,10 +120,12 @@ HB_EXPORT int hb_attention_generic(void* out, const void* q, int q_stride, const
                                    const int* seq_of_token, const int* positions, int T, int nh,
                                    int nkv, int hd, int vd, int page_size, int window, float scale,
                                    const float* slopes, int sink, const void* gate,
-                                   int gate_stride, int act_dt, cudaStream_t stream) {
+                                   int gate_stride, const float* bias_table, int bias_rows,
+                                   const float* sink_values, int keep_first, int gate_wide, int act_dt,
+                                   cudaStream_t stream) {
   if (T <= 0) return HB_OK;
   if (hd <= 0 || hd > ATTN_MAX_HD || vd <= 0 || vd > ATTN_MAX_HD || nkv <= 0 || nh % nkv != 0 ||
-      page_size <= 0)
+      page_size <= 0 || keep_first < 0 || (bias_table != nullptr && bias_rows <= 0))
     return HB_BAD_ARGUMENT;
   const int n_rows = T * nh;
   const int blocks = (n_rows + ATTN_WARPS - 1) / ATTN_WARPS;
@@ -115,6 +133,7 @@ HB_EXPORT int hb_attention_generic(void* out, const void* q, int q_stride, const
     hb_launch(attention_generic_kernel<TA>, dim3(blocks), dim3(ATTN_WARPS * 32), 0, stream, 
         (TA*)out, (const TA*)q, q_stride, (const TA*)k_pages, (const TA*)v_pages, block_table,
         bt_stride, seq_of_token, positions, n_rows, nh, nkv, hd, vd, page_size, window, scale,
-        slopes, sink, (const TA*)gate, gate_stride));
+        slopes, sink, (const TA*)gate, gate_stride, bias_table, bias_rows, sink_values, keep_first,
+        gate_wide));
   return hb_check_launch();
 }

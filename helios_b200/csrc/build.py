@@ -42,11 +42,13 @@ LIBRARIES: Dict[str, str] = {
     "latent_attention": "latent_attention.cu",
     "delta_rule": "delta_rule.cu",
     "moe": "moe.cu",
+    "ssm": "ssm.cu",
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh"]
 # further files a library's source includes
 _INCLUDES: Dict[str, List[str]] = {"gemm_bf16_noalloc": ["gemm_bf16.cu", "gemm_bf16_noalloc.h"],
                                    "attention_bf16": ["attention_mma.cuh", "attention_options.cuh"],
+                                   "attention_generic": ["attention_options.cuh"],
                                    "attention_tc": ["attention_options.cuh"],
                                    "latent_attention": ["attention_mma.cuh"]}
 

@@ -19,11 +19,12 @@
 
 // ---------------------------------------------------------------- short convolution
 // x [T, ld] (the first `channels` columns), w [channels, taps] (the last column is the
-// current token's), conv state of a slot at state + slot * state_stride: [channels, taps - 1],
+// current token's), bias [channels] or null, conv state of a slot at state + slot * state_stride: [channels, taps - 1],
 // oldest first.  out [T, channels].
 template <typename T>
 __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict__ x, int ld,
-                                        const float* __restrict__ w, const float* __restrict__ state,
+                                        const float* __restrict__ w, const float* __restrict__ bias,
+                                        const float* __restrict__ state,
                                         long state_stride, const int* __restrict__ seq_of_token,
                                         const int* __restrict__ cu_tokens,
                                         const int* __restrict__ slots, int n_tokens, int channels,
@@ -37,7 +38,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
     const int s = seq_of_token[t];
     const int local = t - cu_tokens[s];
     const float* st = state + (size_t)slots[s] * state_stride + (size_t)c * (taps - 1);
-    float acc = 0.f;
+    float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int src = local - (taps - 1) + j;
       const float v = src >= 0 ? to_float(x[(size_t)(t - (taps - 1) + j) * ld + c])
@@ -71,7 +72,8 @@ __global__ void causal_conv_state_kernel(float* __restrict__ state, long state_s
   }
 }
 
-HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float* w, float* state,
+HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float* w, const float* bias,
+                                  float* state,
                                   long state_stride, const int* seq_of_token, const int* cu_tokens,
                                   const int* slots, int n_tokens, int n_seqs, int channels, int taps,
                                   int act_dt, cudaStream_t stream) {
@@ -82,7 +84,7 @@ HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float*
   if (blocks > 148 * 16) blocks = 148 * 16;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(causal_conv_silu_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out,
-              (const TA*)x, ld, w, (const float*)state, state_stride, seq_of_token, cu_tokens, slots,
+              (const TA*)x, ld, w, bias, (const float*)state, state_stride, seq_of_token, cu_tokens, slots,
               n_tokens, channels, taps));
   if (taps > 1) {
     const size_t total2 = (size_t)n_seqs * channels;

@@ -175,6 +175,117 @@ HB_EXPORT int hb_add_rmsnorm(void* out, float* residual, const void* delta, cons
   return hb_check_launch();
 }
 
+// ---------------------------------------------------------------- add + two RMSNorms of one row
+// A block whose mixer and feed-forward each read a norm of their own of the SAME stream:
+//   residual[r] += a[r] + b[r]                       (float32; a, b optional: what the block before left)
+//   out1[r] = residual[r] * rstd * w1,   out2[r] = residual[r] * rstd * w2      (out2 / w2 optional)
+// with one rstd = rsqrt(mean(residual[r]^2) + eps) for both.  The row stays in registers (whole
+// groups of four) or is read again (other widths).
+template <typename TA, bool VEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_pair_kernel(TA* __restrict__ out1, TA* __restrict__ out2, float* __restrict__ residual,
+                        const TA* __restrict__ a, const TA* __restrict__ b,
+                        const float* __restrict__ w1, const float* __restrict__ w2, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float* res = residual + (size_t)r * H;
+  const TA* ar = a ? a + (size_t)r * H : nullptr;
+  const TA* br = b ? b + (size_t)r * H : nullptr;
+  const bool write_back = ar != nullptr || br != nullptr;
+  TA* o1 = out1 + (size_t)r * H;
+  TA* o2 = out2 ? out2 + (size_t)r * H : nullptr;
+  float ss = 0.f;
+  if constexpr (VEC) {
+    float v[NORM_GROUPS][4];
+#pragma unroll
+    for (int g = 0; g < NORM_GROUPS; ++g) {
+      const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+      if (c < H) load4(res + c, v[g]);
+    }
+    if (write_back) {
+#pragma unroll
+      for (int g = 0; g < NORM_GROUPS; ++g) {
+        const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+        if (c < H) {
+          float add[4] = {0.f, 0.f, 0.f, 0.f}, x[4];
+          if (ar) { load4(ar + c, x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) add[e] = x[e]; }
+          if (br) { load4(br + c, x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) add[e] += x[e]; }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[g][e] += add[e];
+          store4(res + c, v[g]);
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < NORM_GROUPS; ++g) {
+      const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+      if (c < H) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(v[g][e], v[g][e], ss);
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+#pragma unroll
+    for (int g = 0; g < NORM_GROUPS; ++g) {
+      const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+      if (c < H) {
+        float w[4], y[4];
+        load4(w1 + c, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = v[g][e] * rstd * w[e];
+        store4(o1 + c, y);
+        if (o2) {
+          load4(w2 + c, w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) y[e] = v[g][e] * rstd * w[e];
+          store4(o2 + c, y);
+        }
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float v = res[c];
+      if (write_back) {
+        float add = ar ? to_float(ar[c]) : 0.f;
+        if (br) add += to_float(br[c]);
+        v += add;
+        res[c] = v;
+      }
+      ss = fmaf(v, v, ss);
+    }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const float v = res[c];          // this thread's own write, or the row as it was
+      o1[c] = from_float<TA>(v * rstd * w1[c]);
+      if (o2) o2[c] = from_float<TA>(v * rstd * w2[c]);
+    }
+  }
+}
+
+HB_EXPORT int hb_add_rmsnorm_pair(void* out1, void* out2, float* residual, const void* a, const void* b,
+                                  const float* w1, const float* w2, int n_rows, int H, float eps,
+                                  int act_dt, cudaStream_t stream) {
+  if (n_rows <= 0) return HB_OK;
+  if (H <= 0 || out1 == nullptr || w1 == nullptr || ((out2 == nullptr) != (w2 == nullptr)))
+    return HB_BAD_ARGUMENT;
+  const bool vec = (H % 4 == 0) && H <= NORM_THREADS * NORM_GROUPS * 4 && ((uintptr_t)out1 % 16 == 0) &&
+                   ((uintptr_t)out2 % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
+                   ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)w1 % 16 == 0) &&
+                   ((uintptr_t)w2 % 16 == 0) && (act_dt == HB_F32 || H % 8 == 0);
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    if (vec) hb_launch(add_rmsnorm_pair_kernel<TA, true>, dim3(n_rows), dim3(NORM_THREADS), 0, stream,
+                       (TA*)out1, (TA*)out2, residual, (const TA*)a, (const TA*)b, w1, w2, H, eps);
+    else hb_launch(add_rmsnorm_pair_kernel<TA, false>, dim3(n_rows), dim3(NORM_THREADS), 0, stream,
+                   (TA*)out1, (TA*)out2, residual, (const TA*)a, (const TA*)b, w1, w2, H, eps));
+  return hb_check_launch();
+}
+
 // ---------------------------------------------------------------- plain RMSNorm of act rows
 template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x,
@@ -875,5 +986,158 @@ HB_EXPORT int hb_qk_norm_kv_write(void* rows, int ld, const int* positions, cons
     hb_launch(qk_norm_kv_write_kernel<TA>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (TA*)rows, ld,
               positions, seq_of_token, block_table, bt_stride, (TA*)k_pages, (TA*)v_pages, T, nh, nkv,
               hd, vd, wq, wk, eps, coef, every, page_size, write_cache));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- rotation, q/k norm, cache write
+// rows: [T, ld] with q heads (nh * hd) from column 0, then k heads (nkv * hd); value heads
+// (nkv * vd) at column v_col, or, with v_col < 0, the values ARE the keys as projected (before
+// rotation and norm; vd = hd).  One warp per (token, head):
+//   a q or k head is rotated on its first `rot` values (value i paired with value i + rot/2,
+//   (u, v) -> (u cos - v sin, v cos + u sin), cos/sin [T, rot/2] float32; rot 0: none), then,
+//   with `norm`, divided by its root mean square over hd (eps inside the root) and multiplied
+//   by a weight per channel (wq / wk, null: none);
+//   q is written back in place; k goes to the token's place in the key pages, the values to
+//   the value pages (pages: [page, kv head, slot, hd] and [.., vd]).
+// All arithmetic float32.  Without `write_cache` k is written back in place and no value moves.
+constexpr int QKR_WARPS = 4;
+constexpr int QKR_MAX_HD = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(QKR_WARPS * 32)
+qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
+                            const float* __restrict__ sin_tab, int rot, const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                            int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens,
+                            int nh, int nkv, int hd, int vd, int norm, const float* __restrict__ wq,
+                            const float* __restrict__ wk, float eps, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float head_sm[QKR_WARPS][QKR_MAX_HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = nh + nkv + (v_col >= 0 ? nkv : 0);
+  const long item = (long)blockIdx.x * QKR_WARPS + warp;
+  if (item >= (long)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), h = (int)(item - (long)t * per_token);
+  const int pos = positions[t];
+  T* row = rows + (size_t)t * ld;
+  size_t page_base = 0;
+  int slot = 0;
+  if (write_cache && h >= nh) {
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    slot = pos % page_size;
+    page_base = (size_t)page * nkv;
+  }
+  if (h >= nh + nkv) {                       // a value head with columns of its own
+    if (!write_cache) return;
+    const int g = h - nh - nkv;
+    const T* src = row + v_col + (size_t)g * vd;
+    T* dst = v_pages + ((page_base + g) * page_size + slot) * vd;
+    for (int d = lane; d < vd; d += 32) dst[d] = src[d];
+    return;
+  }
+  const bool is_q = h < nh;
+  T* x = row + (size_t)h * hd;
+  float* xs = head_sm[warp];
+  if (!is_q && write_cache && v_col < 0) {   // the values are the keys as projected
+    T* dst = v_pages + ((page_base + (h - nh)) * page_size + slot) * vd;
+    for (int d = lane; d < hd; d += 32) { const T v = x[d]; dst[d] = v; xs[d] = to_float(v); }
+  } else {
+    for (int d = lane; d < hd; d += 32) xs[d] = to_float(x[d]);
+  }
+  __syncwarp();
+  const int half = rot >> 1;
+  const float* cr = cos_tab ? cos_tab + (size_t)t * half : nullptr;
+  const float* sr = sin_tab ? sin_tab + (size_t)t * half : nullptr;
+  constexpr int PER = QKR_MAX_HD / 32;
+  float y[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = lane + 32 * i;
+    float v = 0.f;
+    if (d < hd) {
+      v = xs[d];
+      if (d < rot) {
+        const int j = d < half ? d : d - half;
+        const float c = cr[j], s = sr[j];
+        v = d < half ? v * c - xs[d + half] * s : v * c + xs[d - half] * s;
+      }
+    }
+    y[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  float f = 1.f;
+  if (norm) f = rsqrtf(warp_sum(ss) / (float)hd + eps);
+  const float* w = is_q ? wq : wk;
+  T* dst = x;
+  if (!is_q && write_cache) dst = k_pages + ((page_base + (h - nh)) * page_size + slot) * hd;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = lane + 32 * i;
+    if (d < hd) {
+      float v = y[i] * f;
+      if (norm && w) v *= w[d];
+      dst[d] = from_float<T>(v);
+    }
+  }
+}
+
+HB_EXPORT int hb_qk_rotate_norm_write(void* rows, int ld, int v_col, const float* cos_tab,
+                                      const float* sin_tab, int rot, const int* positions,
+                                      const int* seq_of_token, const int* block_table, int bt_stride,
+                                      void* k_pages, void* v_pages, int T, int nh, int nkv, int hd, int vd,
+                                      int norm, const float* wq, const float* wk, float eps, int page_size,
+                                      int write_cache, int act_dt, cudaStream_t stream) {
+  if (T <= 0) return HB_OK;
+  if (nh <= 0 || nkv <= 0 || hd <= 0 || hd > QKR_MAX_HD || vd <= 0 || page_size <= 0 || rot < 0 ||
+      rot > hd || rot % 2 || (rot > 0 && (cos_tab == nullptr || sin_tab == nullptr)) ||
+      (v_col < 0 && vd != hd) || (long)(nh + nkv) * hd > ld || (v_col >= 0 && (long)v_col + (long)nkv * vd > ld))
+    return HB_BAD_ARGUMENT;
+  const long items = (long)T * (nh + nkv + (v_col >= 0 ? nkv : 0));
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(qk_rotate_norm_write_kernel<TA>, dim3((unsigned)((items + QKR_WARPS - 1) / QKR_WARPS)),
+              dim3(QKR_WARPS * 32), 0, stream, (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, positions,
+              seq_of_token, block_table, bt_stride, (TA*)k_pages, (TA*)v_pages, T, nh, nkv, hd, vd, norm,
+              wq, wk, eps, page_size, write_cache));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- activations of one argument
+// out = act(x), element by element, float32 arithmetic: 0 the square of relu, 1 silu,
+// 2 gelu (tanh form), 3 x * sigmoid(gate) with `gate` [T, >= W] rows gate_ld apart.
+enum { ACT_RELU2 = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID_GATE = 3 };
+
+template <typename T>
+__global__ void unary_act_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ gate,
+                                 int gate_ld, size_t total, int W, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const float v = to_float(x[idx]);
+    float y;
+    if (kind == ACT_RELU2) { const float r = fmaxf(v, 0.f); y = r * r; }
+    else if (kind == ACT_SILU) y = v / (1.f + expf(-v));
+    else if (kind == ACT_GELU_TANH) y = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    else {
+      const size_t t = idx / W;
+      const float g = to_float(gate[t * (size_t)gate_ld + (idx - t * W)]);
+      y = v / (1.f + expf(-g));
+    }
+    out[idx] = from_float<T>(y);
+  }
+}
+
+HB_EXPORT int hb_unary_act(void* out, const void* x, const void* gate, int gate_ld, int T, int W, int kind,
+                           int act_dt, cudaStream_t stream) {
+  if (T <= 0 || W <= 0) return HB_OK;
+  if (kind < 0 || kind > 3 || (kind == ACT_SIGMOID_GATE && gate == nullptr)) return HB_BAD_ARGUMENT;
+  const size_t total = (size_t)T * W;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(unary_act_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out, (const TA*)x,
+              (const TA*)gate, gate_ld, total, W, kind));
   return hb_check_launch();
 }

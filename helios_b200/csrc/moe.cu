@@ -46,18 +46,29 @@ __device__ __forceinline__ void moe_store4(T* p, const float (&f)[4]) {
   }
 }
 
-enum { MOE_SIGMOID = 0, MOE_SOFTMAX = 1 };
-enum { MOE_GATE_SILU = 0, MOE_GATE_CLAMPED_SWISH = 2 };     // the codes of the gated activations
+// MOE_TOP_SOFTMAX: the choice goes by the logits themselves and the weights are a softmax over
+// the CHOSEN logits alone.  `bias` (a vector the checkpoint brings) is added to the logits
+// before anything else, whatever the kind.
+enum { MOE_SIGMOID = 0, MOE_SOFTMAX = 1, MOE_TOP_SOFTMAX = 2 };
+// the codes of the gated activations; MOE_ACT_RELU2: an expert WITHOUT a gate,
+// down(relu(up x)^2), whose first matrix has ff rows instead of 2 ff
+enum { MOE_GATE_SILU = 0, MOE_GATE_CLAMPED_SWISH = 2, MOE_ACT_RELU2 = 3 };
 
 __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weights,
-                                const float* __restrict__ logits,
-                                const float* __restrict__ correction, int n_tokens, int experts,
+                                const float* __restrict__ logits_in,
+                                const float* __restrict__ correction, const float* __restrict__ bias,
+                                float* __restrict__ biased, int n_tokens, int experts,
                                 int top, int kind) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tokens) return;
-  const float* z = logits + (size_t)t * experts;
+  const float* z = logits_in + (size_t)t * experts;
+  if (bias) {                       // the logits with their bias, in the caller's scratch rows
+    float* zb = biased + (size_t)t * experts;
+    for (int e = 0; e < experts; ++e) zb[e] = z[e] + bias[e];
+    z = zb;
+  }
   // softmax: the scores need the row's maximum and sum (float32, experts in their order)
   float zmax = 0.f, denom = 1.f;
   if (kind == MOE_SOFTMAX) {
@@ -67,8 +78,9 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
     for (int e = 0; e < experts; ++e) denom += expf(z[e] - zmax);
   }
   // sigmoid scores without a correction are ordered as z is, which does not saturate
-  const bool by_logit = (kind == MOE_SIGMOID) && (correction == nullptr);
+  const bool by_logit = ((kind == MOE_SIGMOID) && (correction == nullptr)) || kind == MOE_TOP_SOFTMAX;
   int chosen[MOE_MAX_TOP];
+  float top_logit[MOE_MAX_TOP];
   for (int k = 0; k < top; ++k) {
     float best = 0.f, best_score = 0.f;
     int at = -1;
@@ -76,13 +88,20 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= (chosen[j] == e);
       if (taken) continue;
-      const float s = (kind == MOE_SOFTMAX) ? expf(z[e] - zmax) / denom : 1.f / (1.f + expf(-z[e]));
+      const float s = (kind == MOE_SOFTMAX) ? expf(z[e] - zmax) / denom
+                      : (kind == MOE_TOP_SOFTMAX ? z[e] : 1.f / (1.f + expf(-z[e])));
       const float c = by_logit ? z[e] : s + (correction ? correction[e] : 0.f);
       if (at < 0 || c > best) { best = c; best_score = s; at = e; }   // a NaN never wins: `at` stays valid
     }
     chosen[k] = at;
+    top_logit[k] = best_score;
     ids[(size_t)t * top + k] = at;
     weights[(size_t)t * top + k] = best_score;
+  }
+  if (kind == MOE_TOP_SOFTMAX) {    // the first pick holds the largest logit
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) { top_logit[k] = expf(top_logit[k] - top_logit[0]); sum += top_logit[k]; }
+    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = top_logit[k] / sum;
   }
 }
 
@@ -96,7 +115,7 @@ constexpr int MOE_PER_LANE = 8;
 __global__ void __launch_bounds__(128)
 moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
                      const float* __restrict__ logits, const float* __restrict__ correction,
-                     int n_tokens, int experts, int top, int kind) {
+                     const float* __restrict__ bias, int n_tokens, int experts, int top, int kind) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -108,10 +127,10 @@ moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
 #pragma unroll
   for (int i = 0; i < MOE_PER_LANE; ++i) {
     const int e = lane + 32 * i;
-    score[i] = e < experts ? z[e] : -INFINITY;
+    score[i] = e < experts ? z[e] + (bias ? bias[e] : 0.f) : -INFINITY;
     zmax = fmaxf(zmax, score[i]);
   }
-  const bool by_logit = (kind == MOE_SIGMOID) && (correction == nullptr);
+  const bool by_logit = ((kind == MOE_SIGMOID) && (correction == nullptr)) || kind == MOE_TOP_SOFTMAX;
   if (kind == MOE_SOFTMAX) {
     zmax = warp_max(zmax);
     float part = 0.f;
@@ -129,10 +148,11 @@ moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
   for (int i = 0; i < MOE_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     const float logit = score[i];
-    if (kind == MOE_SIGMOID) score[i] = 1.f / (1.f + expf(-logit));
+    if (kind == MOE_SIGMOID) score[i] = 1.f / (1.f + expf(-logit));     // MOE_TOP_SOFTMAX keeps the logit
     choice[i] = by_logit ? logit : score[i] + ((correction && e < experts) ? correction[e] : 0.f);
   }
   unsigned taken = 0;        // bit i: this lane's i-th output is chosen already
+  float first_logit = 0.f, top_sum = 0.f, mine = 0.f;     // MOE_TOP_SOFTMAX: lane k keeps pick k's term
   for (int k = 0; k < top; ++k) {
     float best = 0.f, best_score = 0.f;
     int at = -1;
@@ -157,30 +177,42 @@ moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
       if (wins) { best = ob; best_score = os; at = oa; }
     }
     if (at >= 0 && (at & 31) == lane) taken |= 1u << (at >> 5);
-    if (lane == 0) {
+    if (kind == MOE_TOP_SOFTMAX) {       // picks come largest first; the terms add up in that order
+      if (k == 0) first_logit = best_score;
+      const float term = expf(best_score - first_logit);
+      top_sum += term;
+      if (lane == k) mine = term;
+      if (lane == 0) ids[(size_t)t * top + k] = at;
+    } else if (lane == 0) {
       ids[(size_t)t * top + k] = at;
       weights[(size_t)t * top + k] = best_score;
     }
   }
+  if (kind == MOE_TOP_SOFTMAX && lane < top) weights[(size_t)t * top + lane] = mine / top_sum;
 }
 
+// `biased`: scratch [n_tokens, experts] for the logits with their bias (rows of more than
+// 32 * MOE_PER_LANE router outputs with a bias only)
 HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, const float* correction,
-                          int n_tokens, int experts, int top, int kind, cudaStream_t stream) {
+                          const float* bias, float* biased, int n_tokens, int experts, int top, int kind,
+                          cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP ||
-      (kind != MOE_SIGMOID && kind != MOE_SOFTMAX))
+      (kind != MOE_SIGMOID && kind != MOE_SOFTMAX && kind != MOE_TOP_SOFTMAX) || top > 32)
     return HB_BAD_ARGUMENT;
   if (experts <= 32 * MOE_PER_LANE) {
     hb_launch(moe_topk_warp_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, ids, weights,
-              logits, correction, n_tokens, experts, top, kind);
+              logits, correction, bias, n_tokens, experts, top, kind);
     return hb_check_launch();
   }
+  if (bias != nullptr && biased == nullptr) return HB_BAD_ARGUMENT;
   hb_launch(moe_topk_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids, weights,
-            logits, correction, n_tokens, experts, top, kind);
+            logits, correction, bias, biased, n_tokens, experts, top, kind);
   return hb_check_launch();
 }
 
-// w_gate_up [experts, 2 ff, width] (gate rows, then up rows), w_down [experts, width, ff].
+// w_gate_up [experts, 2 ff, width] (gate rows, then up rows; [experts, ff, width] for experts
+// without a gate), w_down [experts, width, ff].
 // h [T, width] in the activation dtype.  partial [T * top, width] float32.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -209,9 +241,20 @@ moe_expert_rows_kernel(float* __restrict__ partial, const T* __restrict__ h,
     x[c] = to_float(from_float<T>(w_in * to_float(hr[c])));
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-  const T* wg = w_gate_up + (size_t)e * 2 * ff * width;
+  const bool gated = gate_kind != MOE_ACT_RELU2;
+  const T* wg = w_gate_up + (size_t)e * (gated ? 2 : 1) * ff * width;
   for (int f = warp; f < ff; f += n_warps) {
     const T* gr = wg + (size_t)f * width;
+    if (!gated) {                  // the one matrix of an expert without a gate
+      float u = 0.f;
+      for (int c = lane; c < width; c += 32) u = fmaf(to_float(gr[c]), x[c], u);
+      u = warp_sum(u);
+      if (lane == 0) {
+        u = fmaxf(to_float(from_float<T>(u)), 0.f);
+        y[f] = to_float(from_float<T>(u * u));
+      }
+      continue;
+    }
     const T* ur = wg + (size_t)(ff + f) * width;
     float g = 0.f, u = 0.f;
     for (int c = lane; c < width; c += 32) {
@@ -250,7 +293,7 @@ HB_EXPORT int hb_moe_expert_rows(float* partial, const void* h, const void* w_ga
                                  cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   if (top <= 0 || width <= 0 || ff <= 0 || n_real < 0 ||
-      (gate_kind != MOE_GATE_SILU && gate_kind != MOE_GATE_CLAMPED_SWISH))
+      (gate_kind != MOE_GATE_SILU && gate_kind != MOE_GATE_CLAMPED_SWISH && gate_kind != MOE_ACT_RELU2))
     return HB_BAD_ARGUMENT;
   const size_t smem = (size_t)(width + ff) * sizeof(float);
   if (smem > 200 * 1024) return HB_BAD_ARGUMENT;

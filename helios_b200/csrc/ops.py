@@ -113,10 +113,11 @@ def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
 
 
 def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
-                               value_dim: int):
-    """Libraries attention with ``AttentionOptions`` may choose from at these sizes."""
+                               value_dim: int, tiled: bool = True):
+    """Libraries attention with ``AttentionOptions`` may choose from at these sizes (``tiled``:
+    whether the options are ones the tensor-core kernels take)."""
     if dtype != torch.bfloat16 or head_dim not in TILED_HEAD_DIMS or value_dim != head_dim \
-            or not ATTENTION_OPTIONS_TILED:
+            or not ATTENTION_OPTIONS_TILED or not tiled:
         return ("attention_generic",)
     names = ["attention_bf16"]
     if ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
@@ -179,6 +180,63 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ rotary + cache write
+def add_rmsnorm_pair(residual: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
+                     weight1: torch.Tensor, weight2: Optional[torch.Tensor], eps: float,
+                     out_dtype: torch.dtype):
+    """``residual += a + b`` in float32 and in place (each may be None), then TWO RMS norms of
+    the new rows with one 1 / rms: (residual / rms * weight1, residual / rms * weight2) in
+    ``out_dtype``; ``weight2`` None: the second is None."""
+    _check(residual, "residual", torch.float32, 2)
+    T, H = residual.shape
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _check(t, name, out_dtype, 2)
+            if tuple(t.shape) != (T, H):
+                raise KernelError(f"{name} {tuple(t.shape)} does not fit the residual {(T, H)}")
+    for name, w in (("weight1", weight1), ("weight2", weight2)):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.numel() != H:
+                raise KernelError(f"{name} has {w.numel()} entries for rows of {H}")
+    out1 = torch.empty((T, H), dtype=out_dtype, device=residual.device)
+    out2 = torch.empty((T, H), dtype=out_dtype, device=residual.device) if weight2 is not None else None
+    f = _fn("elementwise", "hb_add_rmsnorm_pair",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+             c_int, c_void_p])
+    _run(f(_p(out1), _p(out2), _p(residual), _p(a), _p(b), _p(weight1), _p(weight2), T, H, float(eps),
+           _dt(out_dtype), _stream()), "add_rmsnorm_pair")
+    return out1, out2
+
+
+UNARY_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+
+
+def unary_act(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(x) element by element (float32 arithmetic): "relu2" (the square of relu), "silu",
+    "gelu_tanh" (0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))))."""
+    _check(x, "x", None, 2)
+    if kind not in UNARY_ACTS:
+        raise KernelError(f"activation {kind!r} is not one of {sorted(UNARY_ACTS)}")
+    out = torch.empty_like(x)
+    f = _fn("elementwise", "hb_unary_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), 0, 0, x.shape[0], x.shape[1], UNARY_ACTS[kind], _dt(x.dtype), _stream()), "unary_act")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x * sigmoid(gate), element by element; ``gate`` [T, >= columns of x], a view whose rows
+    may be strided."""
+    _check(x, "x", None, 2)
+    if gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != x.dtype or gate.shape[0] != x.shape[0] \
+            or gate.shape[1] < x.shape[1] or not gate.is_cuda:
+        raise KernelError(f"gate {tuple(gate.shape)} does not fit x {tuple(x.shape)}")
+    out = torch.empty_like(x)
+    f = _fn("elementwise", "hb_unary_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), _p(gate), gate.stride(0), x.shape[0], x.shape[1], 3, _dt(x.dtype), _stream()),
+         "sigmoid_gate")
+    return out
+
+
 def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float = 1.0):
     """cos and sin [T, rot/2] (float32) of position * inv_freq, computed in float64 and
     multiplied by ``factor`` (the attention factor of a scaled encoding; 1 for none)."""
@@ -240,33 +298,91 @@ class AttentionOptions:
     a window; each is off by default.
 
     ``slopes``   float32 [heads]: score - slopes[h] * (query position - key position)
-    ``sink``     the softmax has a key of score 0 that carries no value:
-                 weights exp(s_j) / (1 + sum_j exp(s_j))
+    ``bias_table`` float32 [rows, heads]: score + bias_table[min(distance, rows - 1), h]
+                 (``distance_bias_rows`` makes one from a table of buckets)
+    ``sink``     the softmax has a key that carries no value: weights
+                 exp(s_j) / (exp(sink) + sum_j exp(s_j)); its score is 0, or
+                 ``sink_values[h]`` (float32 [heads]) where given
+    ``keep_first`` with a window: the first ``keep_first`` keys of a request stay visible to
+                 every later token
     ``gate``     [T, >= heads] in the activation dtype, a view whose rows are ``gate_stride``
-                 apart: head h's output at token t is multiplied by sigmoid(gate[t, h])
+                 apart: head h's output at token t is multiplied by sigmoid(gate[t, h]); with
+                 ``gate_wide`` the view is [T, >= heads * value size] and every output value
+                 has a gate of its own
     ``value_dim`` values per head where they differ from the keys' (None: the same)"""
 
-    __slots__ = ("slopes", "sink", "gate", "gate_stride", "value_dim")
+    __slots__ = ("slopes", "sink", "gate", "gate_stride", "value_dim", "bias_table", "sink_values",
+                 "keep_first", "gate_wide")
 
     def __init__(self, slopes: Optional[torch.Tensor] = None, sink: bool = False,
-                 gate: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> None:
-        self.slopes, self.sink, self.gate, self.value_dim = slopes, bool(sink), gate, value_dim
+                 gate: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+                 bias_table: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None,
+                 keep_first: int = 0, gate_wide: bool = False) -> None:
+        self.slopes, self.sink, self.gate, self.value_dim = slopes, bool(sink) or sink_values is not None, gate, value_dim
+        self.bias_table, self.sink_values = bias_table, sink_values
+        self.keep_first, self.gate_wide = int(keep_first or 0), bool(gate_wide)
         self.gate_stride = 0 if gate is None else int(gate.stride(0))
 
     @property
     def plain(self) -> bool:
-        return self.slopes is None and not self.sink and self.gate is None and self.value_dim is None
+        return self.slopes is None and not self.sink and self.gate is None and self.value_dim is None \
+            and self.bias_table is None and not self.keep_first
 
-    def check(self, tokens: int, num_heads: int, like: torch.Tensor) -> None:
+    @property
+    def tiled(self) -> bool:
+        """Whether the tensor-core kernels take these options."""
+        return self.value_dim is None and self.bias_table is None and self.sink_values is None \
+            and not self.keep_first and not self.gate_wide
+
+    def check(self, tokens: int, num_heads: int, like: torch.Tensor, value_dim: int = 0) -> None:
         if self.slopes is not None:
             _check(self.slopes, "slopes", torch.float32, 1)
             if self.slopes.numel() != num_heads:
                 raise KernelError(f"{self.slopes.numel()} slopes for {num_heads} heads")
+        if self.sink_values is not None:
+            _check(self.sink_values, "sink_values", torch.float32, 1)
+            if self.sink_values.numel() != num_heads:
+                raise KernelError(f"{self.sink_values.numel()} sink values for {num_heads} heads")
+        if self.bias_table is not None:
+            _check(self.bias_table, "bias_table", torch.float32, 2)
+            if self.bias_table.shape[1] != num_heads or self.bias_table.shape[0] < 1:
+                raise KernelError(f"bias table {tuple(self.bias_table.shape)} for {num_heads} heads")
+        if self.keep_first < 0:
+            raise KernelError("keep_first must not be negative")
         if self.gate is not None:
             g = self.gate
+            need = num_heads * value_dim if self.gate_wide else num_heads
             if not g.is_cuda or g.dtype != like.dtype or g.dim() != 2 or g.shape[0] != tokens \
-                    or g.shape[1] < num_heads or g.stride(1) != 1:
-                raise KernelError(f"gate must be [{tokens}, >= {num_heads}] {like.dtype} with unit column stride")
+                    or g.shape[1] < need or g.stride(1) != 1:
+                raise KernelError(f"gate must be [{tokens}, >= {need}] {like.dtype} with unit column stride")
+
+
+def distance_bias_rows(table: torch.Tensor, far: float, window: Optional[int] = None) -> torch.Tensor:
+    """The bias of every distance 0, 1, 2, ... from a learned table of buckets ([rows, heads]):
+    with half = rows // 2, a distance n < half has the row n, a larger one the row
+    min(rows - 1, half + floor(ln(n / half) / ln(far / half) * (rows - half))): one row a
+    distance close by, rows that grow logarithmically up to ``far``, the last row beyond.
+    Returns float32 [distances, heads], long enough that every larger distance has the last
+    entry's bias (or ``window`` distances, where nothing beyond is ever asked for): what
+    ``AttentionOptions.bias_table`` takes.  The buckets are found on the host in float64."""
+    import math
+    rows = int(table.shape[0])
+    half = rows // 2
+    if half < 1 or not far > half:
+        raise KernelError(f"a distance-bias table of {rows} rows with far = {far} has no logarithmic part")
+
+    def bucket(n: int) -> int:
+        if n < half:
+            return n
+        return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+    last = int(math.ceil(far)) + 1          # from ``far`` on the bucket is the last row
+    while bucket(last) != rows - 1:
+        last += 1
+    if window is not None:
+        last = min(last, max(int(window) - 1, 0))
+    index = torch.tensor([bucket(n) for n in range(last + 1)], dtype=torch.long, device=table.device)
+    return table.float().index_select(0, index).contiguous()
 
 
 _NO_OPTIONS = AttentionOptions()
@@ -279,6 +395,9 @@ def _tiled_options(options: Optional[AttentionOptions], tokens: int, num_heads: 
         return _NO_OPTIONS
     if options.value_dim is not None:
         raise KernelError("the tensor-core attention kernels take values of the keys' size only")
+    if not options.tiled:
+        raise KernelError("this tensor-core attention kernel takes no bias table, sink values, kept first "
+                          "keys or gate per value")
     options.check(tokens, num_heads, like)
     return options
 
@@ -307,7 +426,7 @@ def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     T = qkv.shape[0]
     opt = options or _NO_OPTIONS
     vd = opt.value_dim or head_dim
-    opt.check(T, num_heads, qkv)
+    opt.check(T, num_heads, qkv, vd)
     if not 0 < vd <= 256 or tuple(v_pages.shape[1:]) != (num_kv_heads, page_size, vd):
         raise KernelError(f"v_pages has shape {tuple(v_pages.shape)}, expected "
                           f"[pages, {num_kv_heads}, {page_size}, {vd}] with at most 256 values a head")
@@ -315,11 +434,13 @@ def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     f = _fn("attention_generic", "hb_attention_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
-             c_int, c_int, c_void_p])
+             c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
            block_table.shape[1], _p(seq_of_token), _p(positions), T, num_heads, num_kv_heads,
            head_dim, vd, page_size, int(window or 0), float(scale), _p(opt.slopes), int(opt.sink),
-           _p(opt.gate), opt.gate_stride, _dt(qkv.dtype), _stream()),
+           _p(opt.gate), opt.gate_stride, _p(opt.bias_table),
+           0 if opt.bias_table is None else opt.bias_table.shape[0], _p(opt.sink_values),
+           opt.keep_first if window else 0, 1 if opt.gate_wide else 0, _dt(qkv.dtype), _stream()),
          "attention_generic")
     return out
 
@@ -1187,10 +1308,16 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
     for portions, the ``mma.sync`` kernel for the sizes that one does not take.  Everything
     else, and float32, runs one warp a (token, head)."""
     tiled = (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
-             and options.value_dim is None)
+             and options.tiled)
     decode = tiled and ctx.decode_only and num_heads // num_kv_heads <= 16
     fused = None
-    if prepare is not None:
+    if isinstance(prepare, RotateNormPrepare):
+        pr = prepare
+        qk_rotate_norm_write(qkv, pr.cos, pr.sin, ctx.positions, ctx.seq_of_token, block_table, k_pages,
+                             v_pages, num_heads, num_kv_heads, head_dim, options.value_dim or head_dim,
+                             page_size, pr.norm, pr.q_weight, pr.k_weight, pr.eps, pr.value_col,
+                             write_cache=pr.write)
+    elif prepare is not None:
         wq, wk, eps, coef, every, write = prepare
         if decode and write and ATTENTION_DECODE_QK_NORM and qkv.is_contiguous():
             fused = (wq, wk, eps, coef, every)
@@ -1221,6 +1348,73 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
                                       window, scale, options=options)
     return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
                              num_heads, num_kv_heads, head_dim, page_size, window, scale, options)
+
+
+class RotateNormPrepare:
+    """What the rows of a fused projection still want before attention (``attention``'s
+    ``prepare``): a rotation of q and k by ``cos`` / ``sin`` ([T, rot/2] float32, value i of a
+    head paired with value i + rot/2; None: no rotation), then, with ``norm``, the division of
+    every q and k head by its root mean square (eps inside the root) and optional weights per
+    channel; the keys go to the key pages and the values to the value pages: from the columns
+    at ``value_col``, or, with ``value_col`` None, the values ARE the keys as projected, before
+    rotation and norm."""
+
+    __slots__ = ("cos", "sin", "norm", "q_weight", "k_weight", "eps", "value_col", "write")
+
+    def __init__(self, cos=None, sin=None, norm: bool = True, q_weight=None, k_weight=None,
+                 eps: float = 1e-6, value_col: Optional[int] = None, write: bool = True) -> None:
+        self.cos, self.sin, self.norm = cos, sin, bool(norm)
+        self.q_weight, self.k_weight, self.eps = q_weight, k_weight, float(eps)
+        self.value_col, self.write = value_col, bool(write)
+
+
+def qk_rotate_norm_write(rows: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                         positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                         k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], num_heads: int,
+                         num_kv_heads: int, head_dim: int, value_dim: int, page_size: int, norm: bool,
+                         q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                         value_col: Optional[int], write_cache: bool = True) -> None:
+    """See ``RotateNormPrepare``: rows [T, ld] hold q heads, then k heads, from column 0; q is
+    rotated and normed in place, k rotated and normed into the key pages (in place without
+    ``write_cache``), the values copied into the value pages.  float32 arithmetic."""
+    _check(rows, "rows", None, 2)
+    T, ld = rows.shape
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    rot = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[0] != T:
+            raise KernelError(f"cos/sin tables {tuple(cos.shape)}/{tuple(sin.shape)} do not match {T} tokens")
+        rot = 2 * cos.shape[1]
+        if rot > head_dim:
+            raise KernelError(f"rotary dimension {rot} exceeds head_dim {head_dim}")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.numel() != head_dim:
+                raise KernelError(f"{name} has {w.numel()} entries for heads of {head_dim}")
+    if head_dim > 256:
+        raise KernelError(f"heads of {head_dim} values are not supported (at most 256)")
+    if value_col is None and value_dim != head_dim:
+        raise KernelError("values that are the keys have the keys' size")
+    if write_cache:
+        for name, pages, d in (("k_pages", k_pages, head_dim), ("v_pages", v_pages, value_dim)):
+            _check(pages, name, rows.dtype, 4)
+            if tuple(pages.shape[1:]) != (num_kv_heads, page_size, d):
+                raise KernelError(f"{name} has shape {tuple(pages.shape)}, expected "
+                                  f"[pages, {num_kv_heads}, {page_size}, {d}]")
+    f = _fn("elementwise", "hb_qk_rotate_norm_write",
+            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+             c_int, c_int, c_int, c_void_p])
+    _run(f(_p(rows), ld, -1 if value_col is None else int(value_col), _p(cos), _p(sin), rot,
+           _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1],
+           _p(k_pages) if write_cache else 0, _p(v_pages) if write_cache else 0, T, num_heads,
+           num_kv_heads, head_dim, value_dim, 1 if norm else 0, _p(q_weight), _p(k_weight), float(eps),
+           page_size, 1 if write_cache else 0, _dt(rows.dtype), _stream()), "qk_rotate_norm_write")
 
 
 def qk_norm_kv_write(rows: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
@@ -1528,28 +1722,34 @@ def latent_attention(ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch
 
 # ------------------------------------------------------------------ gated delta rule
 def causal_conv_silu(ctx, x: torch.Tensor, channels: int, weight: torch.Tensor,
-                     conv_state: torch.Tensor) -> torch.Tensor:
-    """silu of a short causal convolution over time, per channel, of the first ``channels``
-    columns of ``x`` [T, ld]; ``weight`` [channels, taps] float32 (last column: the current
-    token).  ``conv_state`` [slots, channels * (taps - 1)] float32 (rows may be strided) holds
-    every request's last taps - 1 inputs: read for the tokens before the step's first, and
-    left holding the step's last ones."""
+                     conv_state: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     col0: int = 0) -> torch.Tensor:
+    """silu of a short causal convolution over time, per channel, of the ``channels`` columns
+    of ``x`` [T, ld] from column ``col0`` on; ``weight`` [channels, taps] float32 (last column:
+    the current token), ``bias`` float32 [channels] or None.  ``conv_state`` [slots, channels *
+    (taps - 1)] float32 (rows may be strided) holds every request's last taps - 1 inputs: read
+    for the tokens before the step's first, and left holding the step's last ones."""
     _check(x, "x", None, 2)
     _check(weight, "weight", torch.float32, 2)
     taps = weight.shape[1]
-    if weight.shape[0] != channels or x.shape[1] < channels:
-        raise KernelError(f"conv weight {tuple(weight.shape)} / x {tuple(x.shape)} do not fit {channels} channels")
+    if weight.shape[0] != channels or x.shape[1] < col0 + channels or col0 < 0:
+        raise KernelError(f"conv weight {tuple(weight.shape)} / x {tuple(x.shape)} do not fit {channels} "
+                          f"channels from column {col0}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != channels:
+            raise KernelError(f"conv bias has {bias.numel()} entries for {channels} channels")
     if conv_state.dtype != torch.float32 or conv_state.dim() != 2 or conv_state.stride(1) != 1 \
             or conv_state.shape[1] != channels * (taps - 1):
         raise KernelError(f"conv state {tuple(conv_state.shape)} does not fit {channels} channels x {taps - 1}")
     T = x.shape[0]
     out = torch.empty((T, channels), dtype=x.dtype, device=x.device)
     f = _fn("delta_rule", "hb_causal_conv_silu",
-            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(x), x.shape[1], _p(weight), _p(conv_state), conv_state.stride(0),
-           _p(ctx.seq_of_token), _p(ctx.cu_tokens), _p(ctx.slots), T, ctx.num_seqs, channels, taps,
-           _dt(x.dtype), _stream()), "causal_conv_silu")
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x) + col0 * x.element_size(), x.shape[1], _p(weight), _p(bias), _p(conv_state),
+           conv_state.stride(0), _p(ctx.seq_of_token), _p(ctx.cu_tokens), _p(ctx.slots), T, ctx.num_seqs,
+           channels, taps, _dt(x.dtype), _stream()), "causal_conv_silu")
     return out
 
 
@@ -1607,30 +1807,92 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, hea
     return out
 
 
+def ssm_scan(ctx, xbc: torch.Tensor, offsets, dt_raw: torch.Tensor, a_log: torch.Tensor,
+             dt_bias: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, heads: int, groups: int,
+             n_state: int, head_dim: int) -> torch.Tensor:
+    """The state-space recurrence over the step's tokens, request by request, from the state
+    each request's slot holds (``state`` [slots, heads * n_state * head_dim] float32, rows may be
+    strided; left updated): S <- a S + dt B x^T, y = S^T C + D x with dt = softplus(dt_raw +
+    dt_bias) and a = exp(-exp(a_log) dt) per head.  ``xbc`` [T, .] holds x (heads x head_dim), B
+    and C (groups x n_state each) at the column ``offsets`` (x, B, C); ``dt_raw`` [T, >= heads]
+    a view with contiguous rows.  Returns y [T, heads * head_dim] float32."""
+    _check(xbc, "xbc", None, 2)
+    for name, v in (("a_log", a_log), ("dt_bias", dt_bias), ("d_skip", d_skip)):
+        _check(v, name, torch.float32, 1)
+        if v.numel() != heads:
+            raise KernelError(f"{name} has {v.numel()} entries for {heads} heads")
+    if dt_raw.dim() != 2 or dt_raw.stride(1) != 1 or dt_raw.dtype != xbc.dtype or dt_raw.shape[0] != xbc.shape[0] \
+            or dt_raw.shape[1] < heads:
+        raise KernelError(f"dt_raw {tuple(dt_raw.shape)} does not fit xbc {tuple(xbc.shape)}")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 \
+            or state.shape[1] != heads * n_state * head_dim:
+        raise KernelError(f"state {tuple(state.shape)} does not fit {heads} heads of {n_state} x {head_dim}")
+    x_off, b_off, c_off = offsets
+    if heads % groups or n_state > 256 or max(x_off + heads * head_dim, b_off + groups * n_state,
+                                              c_off + groups * n_state) > xbc.shape[1]:
+        raise KernelError("ssm_scan: sizes do not fit (state size at most 256)")
+    T = xbc.shape[0]
+    y = torch.empty((T, heads * head_dim), dtype=torch.float32, device=xbc.device)
+    f = _fn("ssm", "hb_ssm_scan",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(y), _p(xbc), xbc.shape[1], x_off, b_off, c_off, _p(dt_raw), dt_raw.stride(0), _p(a_log),
+           _p(dt_bias), _p(d_skip), _p(state), state.stride(0), _p(ctx.cu_tokens), _p(ctx.slots), T,
+           ctx.num_seqs, heads, groups, n_state, head_dim, _dt(xbc.dtype), _stream()), "ssm_scan")
+    return y
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int,
+                        eps: float) -> torch.Tensor:
+    """v = y * silu(z), then every one of the ``parts`` equal parts of a row divided by its own
+    root mean square (eps inside the root), times ``weight``: the gate comes before the norm.
+    ``y`` float32 [T, inner]; ``z`` [T, >= inner], a view whose rows may be strided; returns
+    [T, inner] in z's dtype."""
+    _check(y, "y", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    T, inner = y.shape
+    if z.dim() != 2 or z.stride(1) != 1 or z.shape[0] != T or z.shape[1] < inner or weight.numel() != inner \
+            or parts <= 0 or inner % parts or not z.is_cuda:
+        raise KernelError(f"gated_group_rmsnorm: y {tuple(y.shape)}, z {tuple(z.shape)}, weight "
+                          f"{weight.numel()}, {parts} parts do not fit")
+    out = torch.empty((T, inner), dtype=z.dtype, device=y.device)
+    f = _fn("ssm", "hb_gated_group_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(y), _p(z), z.stride(0), _p(weight), T, inner, parts, float(eps), _dt(z.dtype),
+           _stream()), "gated_group_rmsnorm")
+    return out
+
+
 # ------------------------------------------------------------------ routed experts
-ROUTER_KINDS = {"sigmoid": 0, "softmax": 1}
+ROUTER_KINDS = {"sigmoid": 0, "softmax": 1, "top_softmax": 2}
 
 
 def moe_topk(logits: torch.Tensor, top: int, kind: str = "sigmoid",
-             correction: Optional[torch.Tensor] = None):
+             correction: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None):
     """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router ``logits``
-    [T, outputs]: scores s = sigmoid(z), or softmax(z) over all outputs; the ``top`` largest
-    s + correction (float32 [outputs]; None: s alone) are chosen, lower index on a tie, largest
-    first; the weight is s itself."""
+    [T, outputs] (+ ``bias``, float32 [outputs], added first).  Kinds "sigmoid" and "softmax":
+    scores s = sigmoid(z), or softmax(z) over all outputs; the ``top`` largest s + correction
+    (float32 [outputs]; None: s alone) are chosen, lower index on a tie, largest first; the
+    weight is s itself.  Kind "top_softmax": the ``top`` largest logits are chosen and the
+    weights are the softmax over the chosen logits alone."""
     _check(logits, "logits", torch.float32, 2)
     T, E = logits.shape
     if kind not in ROUTER_KINDS:
         raise KernelError(f"router kind {kind!r} is not one of {sorted(ROUTER_KINDS)}")
     if not 0 < top <= min(E, 16):
         raise KernelError(f"top {top} of {E} experts is not supported (1..16)")
-    if correction is not None:
-        _check(correction, "correction", torch.float32, 1)
-        if correction.numel() != E:
-            raise KernelError(f"correction has {correction.numel()} entries for {E} router outputs")
+    for name, v in (("correction", correction), ("bias", bias)):
+        if v is not None:
+            _check(v, name, torch.float32, 1)
+            if v.numel() != E:
+                raise KernelError(f"{name} has {v.numel()} entries for {E} router outputs")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(ids), _p(weights), _p(logits), _p(correction), T, E, top, ROUTER_KINDS[kind], _stream()), "moe_topk")
+    biased = torch.empty_like(logits) if bias is not None and E > 256 else None
+    f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_void_p])
+    _run(f(_p(ids), _p(weights), _p(logits), _p(correction), _p(bias), _p(biased), T, E, top,
+           ROUTER_KINDS[kind], _stream()), "moe_topk")
     return ids, weights
 
 
@@ -1643,6 +1905,9 @@ def moe_topk(logits: torch.Tensor, top: int, kind: str = "sigmoid",
 MOE_GROUPED_MIN_TOKENS = 1
 #: gates an expert may have (codes of ``GLU_KINDS``)
 MOE_GATES = ("silu", "clamped_swish")
+#: activations of an expert WITHOUT a gate, down(act(up x)), whose first matrix has ff rows
+MOE_PLAIN_ACTS = ("relu2",)
+_MOE_ACT_CODES = {"silu": 0, "clamped_swish": 2, "relu2": 3}
 
 
 def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
@@ -1670,7 +1935,7 @@ def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tenso
            _stream()), "moe_scatter_rows")
     offs = ends[:E] if identity else ends
     gate_up = torch._grouped_mm(rows, w_gate_up.transpose(1, 2), offs=offs)
-    y = glu_act(gate_up, gate, limit)
+    y = unary_act(gate_up, gate) if gate in MOE_PLAIN_ACTS else glu_act(gate_up, gate, limit)
     down = torch._grouped_mm(y, w_down.transpose(1, 2), offs=offs)
     out = torch.empty((T, width), dtype=h.dtype, device=h.device)
     f = _fn("moe", "hb_moe_gather_sum",
@@ -1688,7 +1953,8 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     """The sum over a token's chosen experts: of expert(weight * h) with ``weight_on`` =
     "input", of weight * expert(h) with "output".  ``w_gate_up`` [experts, 2 ff, width] (gate
     rows, then up rows), ``w_down`` [experts, width, ff]; ``gate``: "clamped_swish" with its
-    ``limit`` or "silu" (``glu_act``).  Expert ids from ``experts`` up to ``experts + identity``
+    ``limit`` or "silu" (``glu_act``), or "relu2" for experts without a gate, down(relu(up x)^2),
+    whose first matrix is [experts, ff, width].  Expert ids from ``experts`` up to ``experts + identity``
     name experts without tensors, whose output is their input (times the weight).  ``base``
     ([T, width]) is added to the sum.  Returns [T, width] in h's dtype."""
     _check(h, "h", None, 2)
@@ -1698,12 +1964,12 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     _check(w_down, "w_down", h.dtype, 3)
     T, width = h.shape
     E, two_ff, w2 = w_gate_up.shape
-    ff = two_ff // 2
+    ff = two_ff if gate in MOE_PLAIN_ACTS else two_ff // 2
     top = ids.shape[1]
     if w2 != width or tuple(w_down.shape) != (E, width, ff) or tuple(ids.shape) != (T, top) \
             or ids.shape != weights.shape:
         raise KernelError("moe_experts: shapes do not fit")
-    if gate not in MOE_GATES or weight_on not in ("input", "output") or identity < 0:
+    if gate not in MOE_GATES + MOE_PLAIN_ACTS or weight_on not in ("input", "output") or identity < 0:
         raise KernelError(f"moe_experts: gate {gate!r} / weight_on {weight_on!r} / identity {identity}")
     if base is not None:
         _check(base, "base", h.dtype, 2)
@@ -1717,7 +1983,7 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
              c_float, c_int, c_int, c_int, c_int, c_void_p])
     _run(f(_p(partial), _p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), T, top, width, ff,
-           float(limit), GLU_KINDS[gate], 1 if weight_on == "output" else 0, E, _dt(h.dtype), _stream()),
+           float(limit), _MOE_ACT_CODES[gate], 1 if weight_on == "output" else 0, E, _dt(h.dtype), _stream()),
          "moe_expert_rows")
     out = torch.empty((T, width), dtype=h.dtype, device=h.device)
     f = _fn("moe", "hb_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])

@@ -8,6 +8,7 @@ from .mlp import GatedMLP, SwiGLU
 from .moe import RoutedExperts
 from .latent_attention import LatentAttention
 from .delta_rule import GatedDeltaMixer
+from .ssm import SelectiveStateMixer
 from .embedding import LearnedPositions, NormedHead, OutputHead, TokenEmbedding
 from .block import ParallelBlock, PostNormBlock, PreNormBlock
 from .stream import StreamInputMix
@@ -19,4 +20,5 @@ __all__ = ["Block", "DeferredNorm", "FeedForward", "InputStage", "OutputStage", 
            "SwiGLU", "OutputHead", "TokenEmbedding", "PreNormBlock", "ModelPlan", "Run",
            "GatedMLP", "RoutedExperts", "LatentAttention", "GatedDeltaMixer", "PostNormBlock",
            "yarn_frequencies", "yarn_attention_factor", "PendingSum", "StreamStage", "settle", "LayerNorm",
-           "SinkGQAAttention", "distance_slopes", "LearnedPositions", "ParallelBlock", "StreamInputMix"]
+           "SinkGQAAttention", "distance_slopes", "LearnedPositions", "ParallelBlock", "StreamInputMix",
+           "SelectiveStateMixer"]

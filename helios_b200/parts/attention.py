@@ -119,7 +119,7 @@ def distance_slopes(num_heads: int, exponent: float = 8.0):
 
 
 class SinkGQAAttention(Mixer):
-    """Grouped-query attention without rotation whose score carries the position:
+    """Grouped-query attention whose score may carry the position, with a sink in the softmax:
 
         q = norm_q(W_q h) * temp(p),   k = norm_k(W_k h),   v = W_v h
         s_ij = q_i . k_j * scale - slope_h * (i - j)              (j <= i)
@@ -133,13 +133,33 @@ class SinkGQAAttention(Mixer):
     out; the constants are the caller's.  One fused projection gives q | k | v | gate; q and
     k are normed and k and v written into the request's pages by one launch before attention,
     or, in steps of single tokens, inside the decode kernel; the gate is applied where
-    attention writes its output."""
+    attention writes its output.
+
+    Further options, each off by default:
+
+    ``values="keys"``     there is no W_v: v_j = W_k h_j (+ bias) as projected, before any
+                          rotation or norm of the key
+    ``qk_norm="plain"``   q and k are divided by their root mean square without a weight
+    ``position``, ``rotary_dim``  q and k are rotated BEFORE their norm by the tables of this
+                          encoding, on the first ``rotary_dim`` values of a head, value i paired
+                          with value i + rotary_dim / 2
+    ``distance_table``    (rows, far): a learned bias ``rel`` [rows, heads] by the distance i - j,
+                          looked up through ``ops.distance_bias_rows``
+    ``sink="learned"``    the sink's score is a learned number a head (tensor ``sink``) instead of 0
+    ``keep_first``        with ``window``: the request's first ``keep_first`` tokens stay visible
+    ``head_gate="wide"``  W_g has a row per output VALUE, and every value its own gate
+    ``qk_bias``, ``out_bias``  biases of the q and k projections (and v, where it exists) and of
+                          the output projection (``<name>.b``)
+    """
 
     def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 value_dim: Optional[int] = None, qk_norm: bool = True, eps: float = 1e-6,
-                 q_temperature=None, slopes=None, sink: bool = True, head_gate: bool = True,
+                 value_dim: Optional[int] = None, qk_norm=True, eps: float = 1e-6,
+                 q_temperature=None, slopes=None, sink=True, head_gate=True,
                  window: Optional[int] = None,
-                 names=("q", "k", "v", "o", "g", "q.norm", "k.norm")) -> None:
+                 names=("q", "k", "v", "o", "g", "q.norm", "k.norm"), values: str = "projected",
+                 position=None, rotary_dim: int = 0, distance_table=None, keep_first: int = 0,
+                 qk_bias: bool = False, out_bias: bool = False, rel_name: str = "rel",
+                 sink_name: str = "sink", bias_suffix: str = ".b") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
         value_dim = value_dim or head_dim
@@ -147,44 +167,82 @@ class SinkGQAAttention(Mixer):
             raise ValueError(f"heads of {head_dim} / {value_dim} values are not supported (at most 256)")
         if slopes is not None and len(slopes) != num_heads:
             raise ValueError(f"{len(slopes)} slopes for {num_heads} heads")
+        if values not in ("projected", "keys") or qk_norm not in (True, False, "plain") \
+                or sink not in (True, False, "learned") or head_gate not in (True, False, "wide"):
+            raise ValueError(f"values {values!r} / qk_norm {qk_norm!r} / sink {sink!r} / head_gate {head_gate!r}")
+        if values == "keys" and value_dim != head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if (position is None) != (not rotary_dim) or rotary_dim % 2 or rotary_dim > head_dim:
+            raise ValueError(f"a rotation needs an encoding and an even rotary_dim of at most {head_dim}")
+        if keep_first and not window:
+            raise ValueError("first tokens are kept beside a window only")
         self.width, self.num_heads, self.num_kv_heads = width, num_heads, num_kv_heads
         self.head_dim, self.value_dim = head_dim, value_dim
         self.scale, self.eps = float(scale), float(eps)
-        self.qk_norm, self.sink, self.head_gate = bool(qk_norm), bool(sink), bool(head_gate)
+        self.qk_norm, self.sink, self.head_gate = qk_norm, sink, head_gate
         self.q_temperature = None if not q_temperature else (float(q_temperature[0]), int(q_temperature[1]))
         self.slope_values = None if slopes is None else [float(x) for x in slopes]
         self.window = window
         self.names = tuple(names)
-        self.w_in = self.w_o = self.q_weight = self.k_weight = self.slopes = None
+        self.values, self.position, self.rotary_dim = values, position, int(rotary_dim)
+        self.distance_table = None if distance_table is None else (int(distance_table[0]), float(distance_table[1]))
+        self.keep_first = int(keep_first or 0)
+        self.qk_bias, self.out_bias = bool(qk_bias), bool(out_bias)
+        self.rel_name, self.sink_name, self.bias_suffix = rel_name, sink_name, bias_suffix
+        self.w_in = self.b_in = self.w_o = self.b_o = self.q_weight = self.k_weight = self.slopes = None
+        self.bias_rows = self.sink_values = None
         q, kv = num_heads * head_dim, num_kv_heads * head_dim
-        self._gate_col = q + kv + num_kv_heads * value_dim
+        self._value_col = q + kv if values == "projected" else None
+        self._gate_col = q + kv + (num_kv_heads * value_dim if values == "projected" else 0)
+        # the launch that readies q, k and v: the one with weights and temperature, or the one
+        # that also rotates, norms without weights and may take the values from the keys
+        self._rotate_prepare = values == "keys" or position is not None or qk_norm == "plain"
+        if self._rotate_prepare and self.q_temperature is not None:
+            raise ValueError("a query temperature goes with weighted q/k norms and projected values only")
+        self._tiled_options = not (distance_table is not None or sink == "learned" or self.keep_first
+                                   or head_gate == "wide" or value_dim != head_dim)
 
     # ---------------------------------------------------------------- what it keeps
     def cache_spec(self) -> PagedCacheSpec:
         vd = None if self.value_dim == self.head_dim else self.value_dim
-        return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window, value_dim=vd)
+        return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window, value_dim=vd,
+                              keep_first=self.keep_first)
 
     def kernel_libraries(self, dtype):
         return ops.linear_libraries(dtype, self.width) + ops.option_attention_libraries(
-            dtype, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+            dtype, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
+            tiled=self._tiled_options)
 
     # ---------------------------------------------------------------- tensors
     def weight_specs(self) -> Dict[str, WeightSpec]:
         nq, nk, nv, no, ng, nqn, nkn = self.names
         q, kv = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
         specs = {nq: WeightSpec((q, self.width)), nk: WeightSpec((kv, self.width)),
-                 nv: WeightSpec((self.num_kv_heads * self.value_dim, self.width)),
                  no: WeightSpec((self.width, self.num_heads * self.value_dim))}
+        if self.values == "projected":
+            specs[nv] = WeightSpec((self.num_kv_heads * self.value_dim, self.width))
         if self.head_gate:
-            specs[ng] = WeightSpec((self.num_heads, self.width))
-        if self.qk_norm:
+            rows = self.num_heads * (self.value_dim if self.head_gate == "wide" else 1)
+            specs[ng] = WeightSpec((rows, self.width))
+        if self.qk_norm is True:
             specs[nqn] = WeightSpec((self.head_dim,), kind="vector", init="ones_jitter")
             specs[nkn] = WeightSpec((self.head_dim,), kind="vector", init="ones_jitter")
+        if self.qk_bias:
+            for n in (nq, nk) + ((nv,) if self.values == "projected" else ()):
+                specs[n + self.bias_suffix] = WeightSpec((specs[n].shape[0],), kind="vector", init="normal")
+        if self.out_bias:
+            specs[no + self.bias_suffix] = WeightSpec((self.width,), kind="vector", init="normal")
+        if self.distance_table is not None:
+            specs[self.rel_name] = WeightSpec((self.distance_table[0], self.num_heads), kind="vector",
+                                              init="normal", std=0.5)
+        if self.sink == "learned":
+            specs[self.sink_name] = WeightSpec((self.num_heads,), kind="vector", init="normal", std=0.5)
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         nq, nk, nv, no, ng, nqn, nkn = self.names
-        mats = [tensors[nq], tensors[nk], tensors[nv]]
+        order = [nq, nk] + ([nv] if self.values == "projected" else [])
+        mats = [tensors[n] for n in order]
         if self.head_gate:
             mats.append(tensors[ng])
         rows = sum(m.shape[0] for m in mats)
@@ -193,24 +251,47 @@ class SinkGQAAttention(Mixer):
             mats.append(torch.zeros((pad, self.width), dtype=mats[0].dtype, device=mats[0].device))
         self.w_in = torch.cat(mats, dim=0).contiguous()
         self.w_o = tensors[no].contiguous()
-        if self.qk_norm:
+        if self.qk_bias:
+            biases = [tensors[n + self.bias_suffix].float() for n in order]
+            rest = self.w_in.shape[0] - sum(b.numel() for b in biases)
+            biases.append(torch.zeros((rest,), dtype=torch.float32, device=self.w_in.device))
+            self.b_in = torch.cat(biases).contiguous()
+        if self.out_bias:
+            self.b_o = tensors[no + self.bias_suffix].contiguous()
+        if self.qk_norm is True:
             self.q_weight, self.k_weight = tensors[nqn].contiguous(), tensors[nkn].contiguous()
         if self.slope_values is not None:
             self.slopes = torch.tensor(self.slope_values, dtype=torch.float32, device=self.w_o.device)
+        if self.distance_table is not None:
+            self.bias_rows = ops.distance_bias_rows(tensors[self.rel_name], self.distance_table[1], self.window)
+        if self.sink == "learned":
+            self.sink_values = tensors[self.sink_name].contiguous()
 
     # ---------------------------------------------------------------- forward
+    def _options(self, gate) -> "ops.AttentionOptions":
+        return ops.AttentionOptions(slopes=self.slopes, sink=bool(self.sink), gate=gate,
+                                    value_dim=None if self.value_dim == self.head_dim else self.value_dim,
+                                    bias_table=self.bias_rows, sink_values=self.sink_values,
+                                    keep_first=self.keep_first, gate_wide=self.head_gate == "wide")
+
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
-        rows = ops.linear(x, self.w_in)
+        rows = ops.linear(x, self.w_in, self.b_in)
         table = ctx.block_tables[cache.group]
-        coef, every = self.q_temperature or (0.0, 0)
-        gate = rows[:, self._gate_col:self._gate_col + self.num_heads] if self.head_gate else None
-        options = ops.AttentionOptions(slopes=self.slopes, sink=self.sink, gate=gate,
-                                       value_dim=None if self.value_dim == self.head_dim else self.value_dim)
+        gate = None
+        if self.head_gate:
+            n = self.num_heads * (self.value_dim if self.head_gate == "wide" else 1)
+            gate = rows[:, self._gate_col:self._gate_col + n]
+        if self._rotate_prepare:
+            cos, sin = self.position.tables(ctx) if self.position is not None else (None, None)
+            prepare = ops.RotateNormPrepare(cos, sin, bool(self.qk_norm), self.q_weight, self.k_weight, self.eps,
+                                            self._value_col, cache.write)
+        else:
+            coef, every = self.q_temperature or (0.0, 0)
+            prepare = (self.q_weight, self.k_weight, self.eps, coef, every, cache.write)
         attn = ops.attention(ctx, rows, cache.k_pages, cache.v_pages, table, self.num_heads,
                              self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
-                             options=options,
-                             prepare=(self.q_weight, self.k_weight, self.eps, coef, every, cache.write))
-        return ops.linear(attn, self.w_o)
+                             options=self._options(gate), prepare=prepare)
+        return ops.linear(attn, self.w_o, self.b_o)
 
 
 register_part("mixer", "sink_gqa_attention", SinkGQAAttention)

@@ -45,6 +45,7 @@ class PagedCacheSpec:
     window: Optional[int] = None      # None: every key is needed; W: only the last W
     planes: int = 2                   # 2: keys and values; 1: one row a token (a latent cache)
     value_dim: Optional[int] = None   # values per head where they differ from head_dim (planes 2)
+    keep_first: int = 0               # with a window: the request's first tokens stay as well
 
 
 @dataclass(frozen=True)

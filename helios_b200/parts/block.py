@@ -145,12 +145,20 @@ class ParallelBlock(Block):
     sublayers read its output.  ``ls1`` / ``ls2`` are learned per-channel factors
     (``layer_scale``; without it they are 1); the feed-forward may be absent.  The sum is not
     formed here: the block returns its outputs as a ``PendingSum``, and the norm that meets the
-    stream next adds them in float32 in its own kernel."""
+    stream next adds them in float32 in its own kernel.
+
+    With ``ffn_norm`` the feed-forward reads a norm of its own of the SAME stream,
+    x + mult * (ls1 * mixer(norm(x)) + ls2 * feed_forward(ffn_norm(x))); two RMS norms share the
+    row's 1 / rms and run, with the add that was pending, as one kernel (``RMSNorm.add_forward_pair``)."""
 
     def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward] = None, mult: float = 1.0,
                  layer_scale: bool = True, names: Tuple[str, str, str, str, str] =
-                 ("norm1", "mix.", "mlp.", "ls1", "ls2")) -> None:
+                 ("norm1", "mix.", "mlp.", "ls1", "ls2"), ffn_norm: Optional[Norm] = None,
+                 ffn_norm_name: str = "norm2") -> None:
+        if ffn_norm is not None and ffn is None:
+            raise ValueError("a second norm needs a feed-forward to read it")
         self.norm = norm
+        self.ffn_norm, self.ffn_norm_name = ffn_norm, ffn_norm_name
         self._mixer = mixer
         self.ffn = ffn
         self.mult = float(mult)
@@ -168,6 +176,8 @@ class ParallelBlock(Block):
         parts = [(n_norm, self.norm), (n_mix, self._mixer)]
         if self.ffn is not None:
             parts.append((n_ffn, self.ffn))
+        if self.ffn_norm is not None:
+            parts.append((self.ffn_norm_name, self.ffn_norm))
         if self.mixer_scale is not None:
             parts.append((n_ls1, self.mixer_scale))
         if self.ffn_scale is not None:
@@ -182,11 +192,17 @@ class ParallelBlock(Block):
                 state: Optional[torch.Tensor]):
         if isinstance(delta, DeferredNorm):
             raise ValueError("a parallel block takes no deferred norm")
-        h = self.norm.add_forward(residual, delta, ctx.act_dtype)
+        if self.ffn_norm is None:
+            h = h2 = self.norm.add_forward(residual, delta, ctx.act_dtype)
+        elif hasattr(self.norm, "add_forward_pair"):
+            h, h2 = self.norm.add_forward_pair(residual, delta, self.ffn_norm, ctx.act_dtype)
+        else:
+            h = self.norm.add_forward(residual, delta, ctx.act_dtype)
+            h2 = self.ffn_norm.add_forward(residual, None, ctx.act_dtype)
         terms = [(self._mixer.forward(ctx, h, cache, state),
                   self.mixer_scale.scale if self.mixer_scale is not None else None)]
         if self.ffn is not None:
-            terms.append((self.ffn.forward(ctx, h),
+            terms.append((self.ffn.forward(ctx, h2),
                           self.ffn_scale.scale if self.ffn_scale is not None else None))
         return residual, PendingSum(terms, self.mult)
 

@@ -12,11 +12,14 @@ activation and its constants as parameters (the clamped form of ``ops.glu_act`` 
 
 Options, each a constructor parameter with the form above as its default:
 
-``router``      "sigmoid", or "softmax" over ALL router outputs
+``router``      "sigmoid", "softmax" over ALL router outputs, or "top_softmax": the ``top`` largest
+                logits are chosen and the weights are the softmax over the chosen logits alone
+``router_bias`` a vector from the checkpoint that is added to the router's logits (choice and weights)
 ``correction``  a vector from the checkpoint that is added to the scores for the CHOICE only
                 (the weights stay the scores)
 ``weight_on``   "input", or "output": out = sum of s_e * expert_e(h)
-``activation``  "clamped_swish" (with ``limit``) or "silu"
+``activation``  "clamped_swish" (with ``limit``) or "silu"; or "relu2": an expert WITHOUT a gate,
+                down(relu(up x)^2), which has no gate matrix (``names[0]`` is not used)
 ``identity``    this many router outputs beyond the experts stand for experts without
                 tensors whose output is their input
 ``shared_inner`` an expert of this inner size (same form) that every token runs, added to the sum
@@ -37,11 +40,12 @@ class RoutedExperts(FeedForward):
                  names=("gate", "up", "down"), router: str = "sigmoid", correction: bool = False,
                  weight_on: str = "input", activation: str = "clamped_swish", identity: int = 0,
                  shared_inner: Optional[int] = None, correction_name: str = "correction",
-                 shared_prefix: str = "shared.") -> None:
+                 shared_prefix: str = "shared.", router_bias: bool = False,
+                 router_bias_name: str = "router.b") -> None:
         if not 0 < top <= experts + identity:
             raise ValueError(f"top {top} of {experts} + {identity} experts")
         if router not in ops.ROUTER_KINDS or weight_on not in ("input", "output") \
-                or activation not in ops.MOE_GATES:
+                or activation not in ops.MOE_GATES + ops.MOE_PLAIN_ACTS:
             raise ValueError(f"router {router!r} / weight_on {weight_on!r} / activation {activation!r}")
         if identity and weight_on != "output":
             raise ValueError("experts without tensors need the weight on the output")
@@ -52,6 +56,9 @@ class RoutedExperts(FeedForward):
         self.identity, self.shared_inner = int(identity), shared_inner
         self.has_correction, self.correction_name = bool(correction), correction_name
         self.shared_prefix = shared_prefix
+        self.gated = activation not in ops.MOE_PLAIN_ACTS
+        self.has_router_bias, self.router_bias_name = bool(router_bias), router_bias_name
+        self.router_bias = None
         self.w_router = self.w_gate_up = self.w_down = None
         self.correction = self.w_shared_gate_up = self.w_shared_down = None
 
@@ -60,16 +67,20 @@ class RoutedExperts(FeedForward):
         specs = {}
         for e in range(self.experts):
             p = f"{self.expert_prefix}{e}."
-            specs[p + g] = WeightSpec((self.inner, self.width))
+            if self.gated:
+                specs[p + g] = WeightSpec((self.inner, self.width))
             specs[p + u] = WeightSpec((self.inner, self.width))
             specs[p + d] = WeightSpec((self.width, self.inner))
         outputs = self.experts + self.identity
         specs[self.router_name] = WeightSpec((outputs, self.width))
         if self.has_correction:
             specs[self.correction_name] = WeightSpec((outputs,), kind="vector", init="normal")
+        if self.has_router_bias:
+            specs[self.router_bias_name] = WeightSpec((outputs,), kind="vector", init="normal")
         if self.shared_inner:
             p = self.shared_prefix
-            specs[p + g] = WeightSpec((self.shared_inner, self.width))
+            if self.gated:
+                specs[p + g] = WeightSpec((self.shared_inner, self.width))
             specs[p + u] = WeightSpec((self.shared_inner, self.width))
             specs[p + d] = WeightSpec((self.width, self.shared_inner))
         return specs
@@ -81,22 +92,27 @@ class RoutedExperts(FeedForward):
         g, u, d = self.names
         p = self.expert_prefix
         self.w_router = tensors[self.router_name].contiguous()
-        self.w_gate_up = torch.stack([torch.cat([tensors[f"{p}{e}.{g}"], tensors[f"{p}{e}.{u}"]], dim=0)
-                                      for e in range(self.experts)]).contiguous()
+        first = (lambda q: torch.cat([tensors[q + g], tensors[q + u]], dim=0)) if self.gated \
+            else (lambda q: tensors[q + u])
+        self.w_gate_up = torch.stack([first(f"{p}{e}.") for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[f"{p}{e}.{d}"] for e in range(self.experts)]).contiguous()
         if self.has_correction:
             self.correction = tensors[self.correction_name].contiguous()
+        if self.has_router_bias:
+            self.router_bias = tensors[self.router_bias_name].contiguous()
         if self.shared_inner:
             p = self.shared_prefix
-            self.w_shared_gate_up = torch.cat([tensors[p + g], tensors[p + u]], dim=0).contiguous()
+            self.w_shared_gate_up = first(p).contiguous()
             self.w_shared_down = tensors[p + d].contiguous()
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear_logits(x, self.w_router)          # float32 [T, router outputs]
-        ids, weights = ops.moe_topk(logits, self.top, self.router, self.correction)
+        ids, weights = ops.moe_topk(logits, self.top, self.router, self.correction, self.router_bias)
         base = None
         if self.shared_inner:
-            if self.activation == "silu":
+            if not self.gated:
+                inner = ops.unary_act(ops.linear(x, self.w_shared_gate_up), self.activation)
+            elif self.activation == "silu":
                 inner = ops.linear_swiglu(x, self.w_shared_gate_up)
             else:
                 inner = ops.glu_act(ops.linear(x, self.w_shared_gate_up), self.activation, self.limit)

@@ -34,6 +34,22 @@ class RMSNorm(Norm):
             delta = None
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype, rows)
 
+    def add_forward_pair(self, residual, delta, other: "Norm", out_dtype):
+        """``residual += delta`` (a tensor, a ``PendingSum`` or None), then this norm AND
+        ``other`` of the new rows: (self(residual), other(residual)).  Two RMS norms with one
+        eps share the row's 1 / rms, and a pending sum of plain terms rides along: one kernel."""
+        if type(other) is RMSNorm and other.eps == self.eps and other.width == self.width:
+            if isinstance(delta, PendingSum):
+                plain = delta.mult == 1.0 and len(delta.terms) <= 2 and all(s is None for _t, s in delta.terms)
+                if plain:
+                    (a, _), (b, _) = (delta.terms + [(None, None)] * 2)[:2]
+                    return ops.add_rmsnorm_pair(residual, a, b, self.weight, other.weight, self.eps, out_dtype)
+                settle(residual, delta)
+                delta = None
+            return ops.add_rmsnorm_pair(residual, delta, None, self.weight, other.weight, self.eps, out_dtype)
+        first = self.add_forward(residual, delta, out_dtype)
+        return first, other.add_forward(residual, None, out_dtype)
+
     def add_normed(self, residual, y, out_dtype):
         """``y`` None: only the residual in ``out_dtype``."""
         return ops.rmsnorm_add(residual, y, self.weight, self.eps, out_dtype)
