@@ -186,3 +186,43 @@ def model(cfg, t, tokens):
         x = x + add
         after.append(x)
     return rms_norm(x, t["final.norm"], eps) @ t["head"].T, torch.stack(after)
+
+
+def attend_rows(q, q_pos, keys, values, scale, size, keep_first, sink, rel=None, far=None):
+    """Rows of queries against the keys of ONE sequence: q [n, H, d] at positions ``q_pos``,
+    keys / values [L, G, d] (ready: rotated and normed as they are to be used).  Returns the
+    outputs [n, H, d] and the weights [n, H, L]."""
+    n, H, d = q.shape
+    L, G, _ = keys.shape
+    out = torch.zeros(n, H, values.shape[-1], dtype=F64)
+    wts = torch.zeros(n, H, L, dtype=F64)
+    for r in range(n):
+        i = int(q_pos[r])
+        j = torch.arange(L)
+        vis = (j <= i) & ((i - j < size) | (j < keep_first))
+        for hh in range(H):
+            g = hh // (H // G)
+            s = keys[:, g] @ q[r, hh] * scale
+            if rel is not None:
+                s = s + torch.stack([rel[distance_bucket(max(i - int(jj), 0), rel.shape[0], far), hh] for jj in j])
+            w = sink_softmax(s[None, :], vis[None, :], sink[hh])[0]
+            wts[r, hh] = w
+            out[r, hh] = w @ values[:, g]
+    return out, wts
+
+
+def state_space_scan(x, B, C, dt_raw, dt_bias, a_log, d_skip, S0=None):
+    """The recurrence alone: x [T, H, P], B / C [T, G, N], dt_raw [T, H]; returns y [T, H, P]
+    and the last state [H, N, P]."""
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=1e9)
+    a = torch.exp(-torch.exp(a_log) * dt)
+    S = torch.zeros(H, N, P, dtype=F64) if S0 is None else S0.clone()
+    y = torch.zeros(T, H, P, dtype=F64)
+    for t in range(T):
+        for hh in range(H):
+            g = hh // (H // G)
+            S[hh] = a[t, hh] * S[hh] + dt[t, hh] * torch.outer(B[t, g], x[t, hh])
+            y[t, hh] = S[hh].T @ C[t, g] + d_skip[hh] * x[t, hh]
+    return y, S
