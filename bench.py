@@ -337,6 +337,40 @@ def mizerax_configs(size):
     return mz, dense
 
 
+def gebasun_configs(size):
+    """(Gebasun config.json, Mizerax config.json of equal width, heads, KV heads, layers,
+    vocabulary, experts and expert size) at layer sizes of a real model.  Six layers: window
+    attention with a distance-bias table, window attention with kept first tokens, rotation and
+    a gate per value, and the selective state-space mixer (twice the width inside, heads of 64,
+    a state of 128 rows), in that order, twice; every layer with the routed feed-forward and a
+    shared expert.  The Mizerax model beside it is the package's closest: parallel blocks, sink
+    attention with a gate per head, a routed feed-forward with a shared expert; no loop."""
+    if size == "large":
+        width, heads, kv, hd, experts, top, eff, shared, vocab = 2048, 16, 4, 128, 32, 4, 2048, 2048, 32000
+    else:
+        width, heads, kv, hd, experts, top, eff, shared, vocab = 1024, 8, 2, 64, 16, 2, 2048, 2048, 32000
+    mlp = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "bias_max": 512,
+                     "bias_rows": 64, "mask": {"size": 1024}}, "mlp": mlp}
+    att2 = {"type": "attention_2",
+            "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                      "mask": {"size": 1024, "keep_first": 64}, "rot": {"dims": hd // 2, "base": 500000.0}},
+            "mlp": mlp}
+    ssm = {"type": "mamba2",
+           "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+           "mlp": mlp}
+    gb = {"architecture": "Gebasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+          "layers": [dict(l) for l in (att, att2, ssm, att, att2, ssm)]}
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5},
+             "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top},
+                     "shared": {"ff": shared}}}
+    mz = {"architecture": "Mizerax", "vocab": vocab, "width": width, "max_positions": 8192,
+          "norm": {"eps": 1e-5}, "layers": [dict(layer) for _ in range(6)]}
+    return gb, mz
+
+
 def design_configs(size, design="zokelix"):
     """(Zokelix config.json, dense decoder config.json of equal width, head count, layers, vocabulary
     and active feed-forward size) at layer sizes of a real model.  Six layers: attention over a
@@ -344,6 +378,8 @@ def design_configs(size, design="zokelix"):
     dense, the others routed.  ``design`` "mizerax": ``mizerax_configs``."""
     if design == "mizerax":
         return mizerax_configs(size)
+    if design == "gebasun":
+        return gebasun_configs(size)
     if size == "large":
         width, heads, hd, rank, ff, experts, top, eff, vocab = 2048, 16, 128, 512, 8192, 32, 4, 2048, 32000
     else:
@@ -402,7 +438,8 @@ def run_design(args):
     OPS = ["linear", "linear_bf16", "linear_logits", "linear_swiglu", "add_rmsnorm", "rmsnorm_add", "glu_act",
            "embedding", "rotary_table", "attention", "latent_prepare", "head_gemm", "latent_attention",
            "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts",
-           "add_layernorm", "qk_norm_kv_write", "add_table_rows", "cast_rows"]
+           "add_layernorm", "qk_norm_kv_write", "add_table_rows", "cast_rows",
+           "add_rmsnorm_pair", "qk_rotate_norm_write", "ssm_scan", "gated_group_rmsnorm", "unary_act", "sigmoid_gate"]
 
     def op_table(core, entries_fn, reps=3):
         """milliseconds per op name over one step, run kernel by kernel (nested ops count inside
@@ -445,7 +482,7 @@ def run_design(args):
     for size in [s for s in args.design_sizes.split(",") if s]:
         zk, dense = design_configs(size, args.design)
         res = {}
-        for label, cfg in ((args.design, zk), ("dense", dense)):
+        for label, cfg in ((args.design, zk), ("mizerax" if args.design == "gebasun" else "dense", dense)):
             vocab = cfg.get("vocab") or cfg["vocab_size"]
             model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
             batches = [int(b) for b in args.design_batches.split(",")]
@@ -702,7 +739,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--design", default=None, choices=["zokelix", "mizerax"],
+    ap.add_argument("--design", default=None, choices=["zokelix", "mizerax", "gebasun"],
                     help="measure another design of the package beside a dense decoder of equal size "
                          "(prefill, decode, time by op) instead of the default workload")
     ap.add_argument("--design-sizes", default="small,large")

@@ -123,8 +123,12 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const bool whole_pages = page_size % DEC_TILE == 0;
   const int first = whole_pages ? lo - lo % DEC_TILE : lo;
   const int n_keys = pos - first + 1;
+  // The first keys a window keeps (those it has passed) come as tiles of their own BEFORE the
+  // window's: tile t < kept_tiles holds the keys from t * DEC_TILE on, valid below kept_end.
+  const int kept_end = (window > 0 && opt.keep_first > 0) ? min(opt.keep_first, lo) : 0;
+  const int kept_tiles = (kept_end + DEC_TILE - 1) / DEC_TILE;
   // slices of whole tiles
-  const int tiles_total = (n_keys + DEC_TILE - 1) / DEC_TILE;
+  const int tiles_total = kept_tiles + (n_keys + DEC_TILE - 1) / DEC_TILE;
   const int tiles_per_split = (tiles_total + n_splits - 1) / n_splits;
   const int tile_begin = split * tiles_per_split;
   const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
@@ -148,12 +152,15 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     constexpr int CH = HD / 8;
     __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS;
     __nv_bfloat16* vd = kd + TILE_ELEMS;
+    const bool kept = tile < kept_tiles;
+    const int t_first = kept ? tile * DEC_TILE : first + (tile - kept_tiles) * DEC_TILE;
+    const int t_end = kept ? kept_end : k_end, t_lo = kept ? 0 : lo;
     if (whole_pages) {
-      const int key_first = first + tile * DEC_TILE;
+      const int key_first = t_first;
       const int page = table[key_first / page_size];
       const size_t base = ((size_t)(page * nkv + kvh) * page_size + key_first % page_size) * HD + lane * 8;
-      const int rows_valid = k_end - key_first;            // >= 1; rows from there on are zero-filled,
-      const int rows_skipped = lo - key_first;             // and so are rows before the window
+      const int rows_valid = t_end - key_first;            // >= 1; rows from there on are zero-filled,
+      const int rows_skipped = t_lo - key_first;           // and so are rows before the window
 #pragma unroll
       for (int it = 0; it < DEC_TILE * CH / 32; ++it) {
         const int idx = it * 32 + lane;
@@ -166,8 +173,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     int row_id = -1;
     if (lane < DEC_TILE) {
-      const int key = first + tile * DEC_TILE + lane;
-      if (key < k_end) {
+      const int key = t_first + lane;
+      if (key < t_end) {
         const int page = table[key / page_size];
         row_id = (page * nkv + kvh) * page_size + key % page_size;
       }
@@ -343,24 +350,41 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
       for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
-      const int tile_key0 = first + tile * DEC_TILE;
-      if (opt.slopes != nullptr) {
+      const bool kept = tile < kept_tiles;
+      const int tile_key0 = kept ? tile * DEC_TILE : first + (tile - kept_tiles) * DEC_TILE;
+      const int t_end = kept ? kept_end : k_end, t_lo = kept ? 0 : lo;
+      if (opt.bias_table != nullptr) {
+        // a bias looked up by the distance, for every row (head) of the tile
+        const int key0 = tile_key0 + 2 * (lane & 3);
+        const int g0 = lane >> 2;
+#pragma unroll
+        for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < (WIDE ? 4 : 2); ++e) {
+            const int key = key0 + nt * 8 + (e & 1);
+            const int row = g0 + (e >> 1) * 8;
+            const bool ok = key < t_end && key >= t_lo && row < G;
+            s[nt][e] = ok ? fmaf(s[nt][e], scale_log2, attn_table_bias_log2(opt, pos - key, kvh * G + row, nh))
+                          : -INFINITY;
+          }
+        }
+      } else if (opt.slopes != nullptr) {
         // a bias that grows with the distance, for every row (head) of the tile: its value at
         // this thread's first key of the tile, then a constant step per key; masks only in
         // the last tile (keys beyond the token's own) and the first (keys before the window)
         const int key0 = tile_key0 + 2 * (lane & 3);
         const float at0[2] = {-slope_log2[0] * (float)(pos - key0), -slope_log2[1] * (float)(pos - key0)};
-        const bool edge = tile_key0 + DEC_TILE > k_end || tile_key0 < lo;
+        const bool edge = tile_key0 + DEC_TILE > t_end || tile_key0 < t_lo;
 #pragma unroll
         for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
           for (int e = 0; e < (WIDE ? 4 : 2); ++e) {
             const float v = fmaf(s[nt][e], scale_log2, fmaf(slope_log2[e >> 1], (float)(nt * 8 + (e & 1)), at0[e >> 1]));
             const int key = key0 + nt * 8 + (e & 1);
-            s[nt][e] = (!edge || (key < k_end && key >= lo)) ? v : -INFINITY;
+            s[nt][e] = (!edge || (key < t_end && key >= t_lo)) ? v : -INFINITY;
           }
         }
-      } else if (tile_key0 + DEC_TILE > k_end || tile_key0 < lo) {
+      } else if (tile_key0 + DEC_TILE > t_end || tile_key0 < t_lo) {
         // the last tile (keys beyond the token's own) or the first (keys before the window)
         const int key0 = tile_key0 + 2 * (lane & 3);
 #pragma unroll
@@ -368,7 +392,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = key0 + nt * 8 + (e & 1);
-            s[nt][e] = (key < k_end && key >= lo) ? s[nt][e] * scale_log2 : -INFINITY;
+            s[nt][e] = (key < t_end && key >= t_lo) ? s[nt][e] * scale_log2 : -INFINITY;
           }
         }
       } else {
@@ -433,7 +457,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int h = kvh * G + row;
     if (n_splits == 1) {
       out[((size_t)seq * nh + h) * HD + d] =
-          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, h)));
+          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, h, d, HD),
+                                          attn_sink_log2(opt, h)));
     } else if (cluster_merge) {
       // the slices of this (request, KV head) are one thread-block cluster: park the block's
       // partial result in its own shared memory for the merge below
@@ -488,7 +513,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         acc += os[sp] * f;
       }
       out[((size_t)seq * nh + kvh * G + row) * HD + d] =
-          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, kvh * G + row)));
+          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, kvh * G + row, d, HD),
+                                          attn_sink_log2(opt, kvh * G + row)));
     }
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
@@ -501,7 +527,7 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;   // seq * nh + head
-  const float gate_factor = attn_gate_factor(opt, row / nh, (int)(row % nh));
+  const float sink_log2 = attn_sink_log2(opt, (int)(row % nh));
   const float* ml = part_ml + row * n_splits * 2;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
@@ -511,7 +537,9 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
       acc += part_o[(row * n_splits + s) * HD + d] * exp2f(ml[2 * s] - M);
-    out[row * HD + d] = __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, gate_factor));
+    out[row * HD + d] = __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink,
+                                                        attn_gate_factor(opt, row / nh, (int)(row % nh), d, HD),
+                                                        sink_log2));
   }
 }
 
@@ -549,6 +577,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int p_first = sp + t0;
   const int p_last = sp + min(n_tok, t0 + BQ) - 1;
   const int k_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  // the first keys a window keeps: their tiles come before the window's
+  const int keep = window > 0 ? opt.keep_first : 0;
   const int* table = block_table + (size_t)seq * bt_stride;
 
   const int head_local = warp % heads_per_block, sub = warp / heads_per_block;
@@ -580,7 +610,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     for (int idx = threadIdx.x; idx < PRE_TILE * CHUNKS; idx += PRE_WARPS * 32) {
       const int row = idx / CHUNKS, c = idx - row * CHUNKS;
       const int key = kt * PRE_TILE + row;
-      const bool valid = key >= k_min && key <= p_last;
+      const bool valid = (key >= k_min || key < keep) && key <= p_last;
       size_t base = 0;
       if (valid) {
         const int page = table[key / page_size];
@@ -602,16 +632,20 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int w_pmin = sp + t0 + sub * 16, w_pmax = min(w_pmin + 15, p_last);
   const int w_kmin = (window > 0 && w_pmin - window + 1 > 0) ? w_pmin - window + 1 : 0;
 
-  load_tile(kt_begin, 0);
+  // tiles 0 .. kept_tiles - 1 hold kept first keys; then the window's, from kt_begin on
+  const int kept_tiles = min((min(keep, k_min) + PRE_TILE - 1) / PRE_TILE, kt_begin);
+  auto next_tile = [&](int kt) { return (kt + 1 == kept_tiles) ? kt_begin : kt + 1; };
+  const int kt_first = kept_tiles > 0 ? 0 : kt_begin;
+  load_tile(kt_first, 0);
   cp_async_commit();
   int stage = 0;
-  for (int kt = kt_begin; kt < kt_end; ++kt, stage ^= 1) {
-    if (kt + 1 < kt_end) load_tile(kt + 1, stage ^ 1);
+  for (int kt = kt_first; kt < kt_end; kt = next_tile(kt), stage ^= 1) {
+    if (next_tile(kt) < kt_end) load_tile(next_tile(kt), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
     const int key_base = kt * PRE_TILE;
-    if (active && key_base <= w_pmax && key_base + PRE_TILE - 1 >= w_kmin) {
+    if (active && key_base <= w_pmax && (key_base + PRE_TILE - 1 >= w_kmin || key_base < keep)) {
       const __nv_bfloat16* ktile = smem + (size_t)(stage * 2) * TILE_ELEMS;
       const __nv_bfloat16* vtile = ktile + TILE_ELEMS;
       float s[PRE_TILE / 8][4];
@@ -624,8 +658,10 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
         for (int e = 0; e < 4; ++e) {
           const int key = key_base + nt * 8 + c0 + (e & 1);
           const int pr = (e >> 1) ? pr1 : pr0;
-          const bool ok = key <= pr && (window <= 0 || key > pr - window);
-          if (opt.slopes != nullptr)
+          const bool ok = key <= pr && (window <= 0 || key > pr - window || key < keep);
+          if (opt.bias_table != nullptr)
+            s[nt][e] = ok ? fmaf(s[nt][e], scale_log2, attn_table_bias_log2(opt, pr - key, h, nh)) : -INFINITY;
+          else if (opt.slopes != nullptr)
             s[nt][e] = ok ? fmaf(s[nt][e], scale_log2, -head_slope_log2 * (float)(pr - key)) : -INFINITY;
           else
             s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
@@ -648,12 +684,18 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
     const int tl = r ? tl1 : tl0;
     if (tl >= n_tok) continue;
     // attn_finish(1, m, l, ...) is the factor on every value of the row (1 / l without options)
-    const float inv = attn_finish(1.f, m[r], l[r], opt.sink, attn_gate_factor(opt, tok0 + tl, h));
+    const float inv = attn_finish(1.f, m[r], l[r], opt.sink,
+                                  opt.gate_wide ? 1.f : attn_gate_factor(opt, tok0 + tl, h), attn_sink_log2(opt, h));
     __nv_bfloat16* orow = out + ((size_t)(tok0 + tl) * nh + h) * HD;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
+      float g0v = 1.f, g1v = 1.f;
+      if (opt.gate_wide) {
+        g0v = attn_gate_factor(opt, tok0 + tl, h, nt * 8 + c0, HD);
+        g1v = attn_gate_factor(opt, tok0 + tl, h, nt * 8 + c0 + 1, HD);
+      }
       *reinterpret_cast<uint32_t*>(orow + nt * 8 + c0) =
-          pack_bf16(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+          pack_bf16(o[nt][2 * r] * inv * g0v, o[nt][2 * r + 1] * inv * g1v);
     }
   }
 }
@@ -794,11 +836,15 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
                                        float scale, int n_splits, const float* rot_cos,
                                        const float* rot_sin, int write_cache, int warps,
                                        const float* slopes, int sink, const void* gate,
-                                       int gate_stride, const float* norm_wq, const float* norm_wk,
+                                       int gate_stride, const float* bias_table, int bias_rows,
+                                       const float* sink_values, int keep_first, int gate_wide,
+                                       const float* norm_wq, const float* norm_wk,
                                        float norm_eps, float temp_coef, int temp_every,
                                        cudaStream_t stream) {
   if (S <= 0) return HB_OK;
-  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink};
+  if (keep_first < 0 || (bias_table != nullptr && bias_rows <= 0)) return HB_BAD_ARGUMENT;
+  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink, bias_table, bias_rows,
+                           sink_values, window > 0 ? keep_first : 0, gate_wide};
   const QkPrepare prep = {norm_wq, norm_wk, norm_eps, temp_coef, temp_every};
   if ((norm_wq == nullptr) != (norm_wk == nullptr) || temp_every < 0) return HB_BAD_ARGUMENT;
   if (norm_wk != nullptr && !write_cache) return HB_BAD_ARGUMENT;     // a cached key is normed already
@@ -832,9 +878,13 @@ HB_EXPORT int hb_attention_prefill_bf16(void* out, const void* q, int q_stride, 
                                         const int* start_pos, int nh, int nkv, int hd,
                                         int heads_per_block, int token_subtiles, int page_size,
                                         int window, float scale, const float* slopes, int sink,
-                                        const void* gate, int gate_stride, cudaStream_t stream) {
+                                        const void* gate, int gate_stride, const float* bias_table,
+                                        int bias_rows, const float* sink_values, int keep_first,
+                                        int gate_wide, cudaStream_t stream) {
   if (n_tiles <= 0) return HB_OK;
-  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink};
+  if (keep_first < 0 || (bias_table != nullptr && bias_rows <= 0)) return HB_BAD_ARGUMENT;
+  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink, bias_table, bias_rows,
+                           sink_values, window > 0 ? keep_first : 0, gate_wide};
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || heads_per_block < 1 || token_subtiles < 1 ||
       heads_per_block * token_subtiles > PRE_WARPS)
     return HB_BAD_ARGUMENT;

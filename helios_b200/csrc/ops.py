@@ -115,12 +115,12 @@ def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
 def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
                                value_dim: int, tiled: bool = True):
     """Libraries attention with ``AttentionOptions`` may choose from at these sizes (``tiled``:
-    whether the options are ones the tensor-core kernels take)."""
+    whether the options are ones the tcgen05 kernel takes too)."""
     if dtype != torch.bfloat16 or head_dim not in TILED_HEAD_DIMS or value_dim != head_dim \
-            or not ATTENTION_OPTIONS_TILED or not tiled:
+            or not ATTENTION_OPTIONS_TILED:
         return ("attention_generic",)
     names = ["attention_bf16"]
-    if ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
+    if tiled and ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
         names.append("attention_tc")
     return tuple(names)
 
@@ -330,9 +330,15 @@ class AttentionOptions:
 
     @property
     def tiled(self) -> bool:
-        """Whether the tensor-core kernels take these options."""
+        """Whether the tcgen05 prefill kernel takes these options."""
         return self.value_dim is None and self.bias_table is None and self.sink_values is None \
             and not self.keep_first and not self.gate_wide
+
+    @property
+    def tiled_mma(self) -> bool:
+        """Whether the ``mma.sync`` kernels (split-context decode, tiled prefill) take these
+        options: all of them, as long as values have the keys' size."""
+        return self.value_dim is None
 
     def check(self, tokens: int, num_heads: int, like: torch.Tensor, value_dim: int = 0) -> None:
         if self.slopes is not None:
@@ -389,17 +395,24 @@ _NO_OPTIONS = AttentionOptions()
 
 
 def _tiled_options(options: Optional[AttentionOptions], tokens: int, num_heads: int,
-                   like: torch.Tensor) -> AttentionOptions:
-    """Checked options for the tensor-core kernels, whose values have the keys' size."""
+                   like: torch.Tensor, head_dim: int = 0, mma: bool = False) -> AttentionOptions:
+    """Checked options for the tensor-core kernels, whose values have the keys' size (``mma``:
+    for the ``mma.sync`` kernels, which take every other option)."""
     if options is None:
         return _NO_OPTIONS
     if options.value_dim is not None:
         raise KernelError("the tensor-core attention kernels take values of the keys' size only")
-    if not options.tiled:
+    if not (options.tiled_mma if mma else options.tiled):
         raise KernelError("this tensor-core attention kernel takes no bias table, sink values, kept first "
                           "keys or gate per value")
-    options.check(tokens, num_heads, like)
+    options.check(tokens, num_heads, like, head_dim)
     return options
+
+
+def _option_args(opt: AttentionOptions, window: Optional[int]):
+    """The options as the ``mma.sync`` launchers take them, after slopes, sink and gate."""
+    return (_p(opt.bias_table), 0 if opt.bias_table is None else int(opt.bias_table.shape[0]),
+            _p(opt.sink_values), opt.keep_first if window else 0, 1 if opt.gate_wide else 0)
 
 
 def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -1044,7 +1057,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     S = qkv.shape[0]
     if block_table.shape[0] != S or positions.numel() != S:
         raise KernelError("decode attention needs one token per request")
-    opt = _tiled_options(options, S, num_heads, qkv)
+    opt = _tiled_options(options, S, num_heads, qkv, head_dim, mma=True)
     cos = sin = None
     if rotary is not None and rotary[0] is not None:
         cos, sin = rotary
@@ -1086,13 +1099,14 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     f = _fn("attention_bf16", "hb_attention_decode_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int,
-             c_void_p])
+             c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+             c_void_p, c_void_p, c_float, c_float, c_int, c_void_p])
     _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
            _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
            head_dim, page_size, int(window or 0), float(scale), int(n_splits), _p(cos), _p(sin),
            1 if write_cache else 0, int(warps), _p(opt.slopes), int(opt.sink), _p(opt.gate),
-           opt.gate_stride, _p(wq), _p(wk), float(n_eps), float(t_coef), int(t_every), _stream()),
+           opt.gate_stride, *_option_args(opt, window), _p(wq), _p(wk), float(n_eps), float(t_coef),
+           int(t_every), _stream()),
          "attention_decode_bf16")
     return out
 
@@ -1129,16 +1143,17 @@ def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: to
                           f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
     heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
     T = qkv.shape[0]
-    opt = _tiled_options(options, T, num_heads, qkv)
+    opt = _tiled_options(options, T, num_heads, qkv, head_dim, mma=True)
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_prefill_bf16",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-             c_void_p, c_int, c_void_p, c_int, c_void_p])
+             c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
            block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos),
            num_heads, num_kv_heads, head_dim, heads, subtiles, page_size, int(window or 0),
-           float(scale), _p(opt.slopes), int(opt.sink), _p(opt.gate), opt.gate_stride, _stream()),
+           float(scale), _p(opt.slopes), int(opt.sink), _p(opt.gate), opt.gate_stride,
+           *_option_args(opt, window), _stream()),
          "attention_prefill_bf16")
     return out
 
@@ -1308,7 +1323,7 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
     for portions, the ``mma.sync`` kernel for the sizes that one does not take.  Everything
     else, and float32, runs one warp a (token, head)."""
     tiled = (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
-             and options.tiled)
+             and options.tiled_mma)
     decode = tiled and ctx.decode_only and num_heads // num_kv_heads <= 16
     fused = None
     if isinstance(prepare, RotateNormPrepare):
@@ -1335,7 +1350,7 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
                                          None, fused is not None,
                                          decode_warps(ctx.num_seqs * num_kv_heads, splits, head_dim,
                                                       ctx.max_context_len), options=options, qk_norm=fused)
-        if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
+        if (ATTENTION_TCGEN05 and options.tiled and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)
             return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,

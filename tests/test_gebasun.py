@@ -367,7 +367,8 @@ def _paged(keys, values, page, g, dt):
     return kp, vp, order.to(torch.int32)
 
 
-def _attend(ops, q, kp, vp, order, q_pos, nh, nkv, hd, page, scale, window, options, decode, n_keys):
+def _attend(ops, q, kp, vp, order, q_pos, nh, nkv, hd, page, scale, window, options, decode, n_keys,
+            splits=None):
     """The queries as single decoded tokens of requests of their own (``decode``), or as ONE
     portion of consecutive tokens of one request; all read the same pages."""
     from helios_b200.engine.batch import SeqSlice
@@ -382,7 +383,8 @@ def _attend(ops, q, kp, vp, order, q_pos, nh, nkv, hd, page, scale, window, opti
         seq_of, cu = torch.zeros(n, dtype=torch.int32), torch.tensor([0, n], dtype=torch.int32)
         start, seqs = q_pos[:1].clone(), [SeqSlice(None, 0, int(q_pos[0]), n, 0)]
     ctx = SimpleNamespace(seq_of_token=seq_of.to(dev), positions=q_pos.to(dev), start_pos=start.to(dev),
-                          context_len=(q_pos + 1).to(dev) if decode else (q_pos[-1:] + 1).to(dev), extras={},
+                          context_len=(q_pos + 1).to(dev) if decode else (q_pos[-1:] + 1).to(dev),
+                          extras={"decode_splits": splits} if splits else {},
                           max_context_len=n_keys, cu_tokens=cu.to(dev), decode_only=decode,
                           max_tokens_per_seq=1 if decode else n, num_tokens=n, seqs=seqs, num_seqs=len(seqs))
     table = order.view(1, -1).repeat(len(seqs), 1).contiguous().to(dev)
@@ -392,21 +394,24 @@ def _attend(ops, q, kp, vp, order, q_pos, nh, nkv, hd, page, scale, window, opti
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("decode", [True, False])
-@pytest.mark.parametrize("dtype,hd", [("float32", 40), ("bfloat16", 64), ("bfloat16", 32), ("bfloat16", 96),
-                                      ("bfloat16", 48)])
-def test_attention_singles_out_keys_at_every_edge(dtype, hd, decode):
-    """One request of 300 tokens in scrambled pages of 16, a window of 37 and 21 kept first
+@pytest.mark.parametrize("dtype,hd,page", [("float32", 40, 16), ("bfloat16", 64, 16), ("bfloat16", 32, 16),
+                                           ("bfloat16", 96, 16), ("bfloat16", 48, 16), ("bfloat16", 128, 24),
+                                           ("bfloat16", 64, 8), ("bfloat16", 96, 32)])
+def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
+    """One request of 300 tokens in scrambled pages of 16 (or 8, 24, 32), a window of 37 and 21 kept first
     tokens, a bias table, learned sinks and a gate per value.  Every query is aligned with ONE
     key and scaled so that this key, if it is visible, takes nearly all the weight whatever its
     bias: the oldest key inside the window and the one just outside, the last kept token and
     the first that is not, keys at page borders, position 0, the query's own.  A key that is
     NOT visible must leave no trace.  Then queries against which every key scores far below
-    the sink.  Every row also against the plain softmax."""
+    the sink.  Every row also against the plain softmax.  Single tokens in bfloat16 also with
+    the context cut into 1, 3, 5 and 12 slices (the kept tokens then fall into a slice of their
+    own, share one with the window, or are all there is)."""
     from helios_b200.csrc import ops
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(3 + hd)
-    n, page, nh, nkv, W, keep, rows, far = 300, 16, 4, 2, 37, 21, 10, 30.0
+    n, nh, nkv, W, keep, rows, far = 300, 4, 2, 37, 21, 10, 30.0
     keys = torch.randn(n, nkv, hd, generator=g)
     keys[..., -1] = 3.0            # a query along -e_last scores every key far below 0
     keys = (keys / keys.norm(dim=-1, keepdim=True)).to(dt).float()
@@ -445,26 +450,27 @@ def test_attention_singles_out_keys_at_every_edge(dtype, hd, decode):
     flat = ops.distance_bias_rows(rel.cuda(), far, W)
     options = ops.AttentionOptions(bias_table=flat, sink_values=sink.cuda(), keep_first=keep,
                                    gate=gate.cuda()[:, 2:2 + nh * hd], gate_wide=True)
-    out = _attend(ops, q.view(len(q_pos), nh * hd).contiguous(), kp, vp, order, q_pos, nh, nkv, hd, page, 1.0, W,
-                  options, decode, n).view(len(q_pos), nh, hd)
     want, wts = pg.attend_rows(q.double(), q_pos, keys.double(), values.double(), 1.0, W, keep, sink.double(),
                                rel.double(), far)
     gates = torch.sigmoid(gate[:, 2:2 + nh * hd].double()).view(len(q_pos), nh, hd)
     want = want * gates
     tol = 2e-5 if dtype == "float32" else 2e-2
     rep = nh // nkv
-    for r, c in enumerate(chosen):
-        assert (out[r].double() - want[r]).abs().max() < tol * max(1.0, float(want[r].abs().max())), (r, int(q_pos[r]), c)
-        if c == "sink" or (decode and c is None):
-            assert float(wts[r].sum(-1).max()) < 0.01 and float(out[r].abs().max()) < 0.05
-        elif c is not None:
-            key, visible = c
-            if visible:
-                assert float(wts[r, :, key].min()) > 0.99, "the case does not single out its key"
-                lone = values[key].double().repeat_interleave(rep, 0) * gates[r]
-                assert (out[r].double() - lone).abs().max() < 0.05 * float(values.abs().max())
-            else:
-                assert float(wts[r, :, key].max()) == 0.0
+    for splits in ((None, 1, 3, 5, 12) if decode and dtype == "bfloat16" and hd in ops.TILED_HEAD_DIMS else (None,)):
+        out = _attend(ops, q.view(len(q_pos), nh * hd).contiguous(), kp, vp, order, q_pos, nh, nkv, hd, page, 1.0, W,
+                      options, decode, n, splits).view(len(q_pos), nh, hd)
+        for r, c in enumerate(chosen):
+            assert (out[r].double() - want[r]).abs().max() < tol * max(1.0, float(want[r].abs().max())), (r, int(q_pos[r]), c)
+            if c == "sink" or (decode and c is None):
+                assert float(wts[r].sum(-1).max()) < 0.01 and float(out[r].abs().max()) < 0.05
+            elif c is not None:
+                key, visible = c
+                if visible:
+                    assert float(wts[r, :, key].min()) > 0.99, "the case does not single out its key"
+                    lone = values[key].double().repeat_interleave(rep, 0) * gates[r]
+                    assert (out[r].double() - lone).abs().max() < 0.05 * float(values.abs().max())
+                else:
+                    assert float(wts[r, :, key].max()) == 0.0
 
 
 @pytest.mark.gpu
