@@ -1822,6 +1822,10 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, hea
     return out
 
 
+#: requests with at most this many tokens in a step scan straight from the convolution's rows
+SSM_DIRECT_MAX_TOKENS = 4
+
+
 def ssm_scan(ctx, xbc: torch.Tensor, offsets, dt_raw: torch.Tensor, a_log: torch.Tensor,
              dt_bias: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, heads: int, groups: int,
              n_state: int, head_dim: int) -> torch.Tensor:
@@ -1848,6 +1852,25 @@ def ssm_scan(ctx, xbc: torch.Tensor, offsets, dt_raw: torch.Tensor, a_log: torch
         raise KernelError("ssm_scan: sizes do not fit (state size at most 256)")
     T = xbc.shape[0]
     y = torch.empty((T, heads * head_dim), dtype=torch.float32, device=xbc.device)
+    if getattr(ctx, "max_tokens_per_seq", T) > SSM_DIRECT_MAX_TOKENS:
+        # portions of prompts: the inputs as float32 rows first, then the scan that fetches them
+        # a chunk ahead (the same arithmetic in the same order as the kernel below)
+        sizes = (ctypes.c_int * 3)()
+        f = _fn("ssm", "hb_ssm_stage_sizes", [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+        base = ctypes.addressof(sizes)
+        _run(f(heads, groups, n_state, head_dim, base, base + 4, base + 8), "ssm_stage_sizes")
+        bc = torch.empty((T, sizes[0]), dtype=torch.float32, device=xbc.device)
+        xs = torch.empty((T, sizes[1]), dtype=torch.float32, device=xbc.device)
+        da = torch.empty((T, sizes[2]), dtype=torch.float32, device=xbc.device)
+        f = _fn("ssm", "hb_ssm_scan_staged",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                 c_void_p, c_void_p, c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                 c_int, c_int, c_int, c_void_p])
+        _run(f(_p(y), _p(bc), _p(xs), _p(da), _p(xbc), xbc.shape[1], x_off, b_off, c_off, _p(dt_raw),
+               dt_raw.stride(0), _p(a_log), _p(dt_bias), _p(d_skip), _p(state), state.stride(0),
+               _p(ctx.cu_tokens), _p(ctx.slots), T, ctx.num_seqs, heads, groups, n_state, head_dim,
+               _dt(xbc.dtype), _stream()), "ssm_scan_staged")
+        return y
     f = _fn("ssm", "hb_ssm_scan",
             [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])

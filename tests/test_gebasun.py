@@ -478,40 +478,58 @@ def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
 @pytest.mark.parametrize("N,P,H,G", [(16, 24, 4, 2), (7, 15, 2, 1), (48, 40, 6, 3), (130, 33, 2, 2), (64, 64, 4, 1)])
 def test_state_space_scan_in_two_steps_from_slots_used_again(dtype, N, P, H, G):
     """Three requests of unequal length in one batch, each cut into two steps; the slots hold
-    what another request left and are zeroed by hand as the cache manager does at admission."""
+    what another request left and are zeroed by hand as the cache manager does at admission.
+    Once through the kernel for portions (inputs staged, chunks of 16 fetched ahead: the cuts
+    fall inside a chunk, the lengths pass two chunk borders) and once through the kernel for
+    single tokens; the two agree bit for bit."""
     from helios_b200.csrc import ops
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(N + P)
-    lengths, cuts, slots = [37, 1, 20], [17, 1, 3], [2, 0, 3]
+    lengths, cuts, slots = [70, 1, 20], [33, 1, 3], [2, 0, 3]
     ld = H * P + 2 * G * N + 3
-    state = torch.randn(5, H * N * P, generator=g).cuda()
+    state0 = torch.randn(5, H * N * P, generator=g).cuda()
     for s in slots:
-        state[s].zero_()
+        state0[s].zero_()
     data = [torch.randn(L, ld + H, generator=g).to(dt) for L in lengths]
     a_log, dt_bias, d_skip = (torch.randn(H, generator=g) * 0.5 for _ in range(3))
-    outs = [[] for _ in lengths]
-    for step in range(2):
-        parts = [(d[:c] if step == 0 else d[c:]) for d, c in zip(data, cuts)]
-        live = [i for i, p in enumerate(parts) if p.shape[0]]
-        rows = torch.cat([parts[i] for i in live]).cuda()
-        cu = torch.tensor([0] + list(torch.tensor([parts[i].shape[0] for i in live]).cumsum(0)), dtype=torch.int32)
-        ctx = SimpleNamespace(cu_tokens=cu.cuda(), slots=torch.tensor([slots[i] for i in live], dtype=torch.int32).cuda(),
-                              num_seqs=len(live))
-        xbc = rows[:, :ld].contiguous()
-        y = ops.ssm_scan(ctx, xbc, (0, H * P, H * P + G * N), rows[:, ld:], a_log.cuda(), dt_bias.cuda(),
-                         d_skip.cuda(), state, H, G, N, P).cpu()
-        for k, i in enumerate(live):
-            outs[i].append(y[cu[k]:cu[k + 1]])
+    def run(most):
+        """Both steps with requests of more than ``most`` tokens on the kernel for portions."""
+        kept, ops.SSM_DIRECT_MAX_TOKENS = ops.SSM_DIRECT_MAX_TOKENS, most
+        state = state0.clone()
+        outs = [[] for _ in lengths]
+        try:
+            for step in range(2):
+                parts = [(d[:c] if step == 0 else d[c:]) for d, c in zip(data, cuts)]
+                live = [i for i, p in enumerate(parts) if p.shape[0]]
+                rows = torch.cat([parts[i] for i in live]).cuda()
+                cu = torch.tensor([0] + list(torch.tensor([parts[i].shape[0] for i in live]).cumsum(0)),
+                                  dtype=torch.int32)
+                ctx = SimpleNamespace(cu_tokens=cu.cuda(), num_seqs=len(live),
+                                      slots=torch.tensor([slots[i] for i in live], dtype=torch.int32).cuda())
+                xbc = rows[:, :ld].contiguous()
+                y = ops.ssm_scan(ctx, xbc, (0, H * P, H * P + G * N), rows[:, ld:], a_log.cuda(), dt_bias.cuda(),
+                                 d_skip.cuda(), state, H, G, N, P).cpu()
+                for k, i in enumerate(live):
+                    outs[i].append(y[cu[k]:cu[k + 1]])
+        finally:
+            ops.SSM_DIRECT_MAX_TOKENS = kept
+        return [torch.cat(o) for o in outs], state.cpu()
+
+    seen = [run(1 << 30), run(0)]
+    outs, state = seen[1]
+    for a, b in zip(seen[0][0], seen[1][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(seen[0][1], seen[1][1])
     for i, d in enumerate(data):
         d = d.double()
         want, S = pg.state_space_scan(d[:, :H * P].view(-1, H, P), d[:, H * P:H * P + G * N].view(-1, G, N),
                                       d[:, H * P + G * N:H * P + 2 * G * N].view(-1, G, N), d[:, ld:], dt_bias.double(),
                                       a_log.double(), d_skip.double())
-        got = torch.cat(outs[i]).double().view(-1, H, P)
+        got = outs[i].double().view(-1, H, P)
         scale = max(1.0, float(want.abs().max()))
         assert (got - want).abs().max() < 2e-5 * scale, (i, float((got - want).abs().max()))
-        assert (state[slots[i]].cpu().double().view(H, N, P) - S).abs().max() < 2e-5 * max(1.0, float(S.abs().max()))
+        assert (state[slots[i]].double().view(H, N, P) - S).abs().max() < 2e-5 * max(1.0, float(S.abs().max()))
 
 
 @pytest.mark.gpu
