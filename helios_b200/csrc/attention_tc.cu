@@ -34,6 +34,9 @@ constexpr int SOFTMAX_THREADS = 256;
 
 struct AttnArgs {
   AttnOptions opt;          // distance bias, sink, gate (all off when zeroed)
+  const float* bias_t;      // the bias table by distance TRANSPOSED, [heads, opt.bias_rows] (or null): a
+                            // warp's rows are few heads x consecutive tokens, so its look-ups for one
+                            // key fall into a few short runs of one head's row
   __nv_bfloat16* out;
   const __nv_bfloat16* q;
   int q_stride;
@@ -128,8 +131,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int p_last = sp + min(n_tok, t0 + TQ) - 1;
   const int k_min = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
   const int kt_begin = k_min / TILE, kt_end = p_last / TILE + 1;
+  // The first keys a window keeps come as tiles of their own BEFORE the window's: iteration
+  // it < kept_tiles walks tile it, the others the tiles from kt_begin on.
+  const int keep = a.window > 0 ? a.opt.keep_first : 0;
+  const int kept_tiles = min((min(keep, k_min) + TILE - 1) / TILE, kt_begin);
+  auto tile_of = [&](int it) { return it < kept_tiles ? it : kt_begin + it - kept_tiles; };
   // a tile beyond the request's tokens (padding of a captured step's tile list) has no work
-  const int n_it = t0 < n_tok ? kt_end - kt_begin : 0;
+  const int n_it = t0 < n_tok ? kept_tiles + kt_end - kt_begin : 0;
   const int* table = a.block_table + (size_t)seq * a.bt_stride;
   const int ps = a.page_size;
   const int pages_per_tile = TILE / ps;
@@ -148,15 +156,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int full0 = is_v ? 9 : 0, empty0 = is_v ? 11 : 2;
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
-        const int key_base = (kt_begin + it) * TILE;
-        // pages that hold at least one key some row may see (a contiguous run)
-        int first = 0, count = 0;
-        for (int i = 0; i < pages_per_tile; ++i) {
-          const int key0 = key_base + i * ps;
-          const bool valid = key0 + ps - 1 >= k_min && key0 <= p_last;
-          if (valid) { if (count == 0) first = i; ++count; }
-        }
-        const bool mine = lane >= first && lane < first + count;
+        const int key_base = tile_of(it) * TILE;
+        // pages that hold at least one key some row may see: inside the first row's window
+        // or among the kept first keys (pages in between may have been given back)
+        const int key0 = key_base + lane * ps;
+        const bool mine = lane < pages_per_tile && (key0 + ps - 1 >= k_min || key0 < keep) && key0 <= p_last;
+        const int count = __popc(__ballot_sync(0xffffffffu, mine));
         int row = 0;
         if (mine) row = (table[(key_base + lane * ps) / ps] * a.nkv + kvh) * ps;    // before the wait
         int go = 1;
@@ -237,8 +242,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // with a distance bias the scores are scaled and biased as they come out of tensor
     // memory, and the factor on them further down is 1
     const bool biased = a.opt.slopes != nullptr;
+    const bool tabled = a.bias_t != nullptr;
     const float slope_log2 = (biased && row_valid) ? a.opt.slopes[kvh * G + g] * LOG2E : 0.f;
-    const float sc = biased ? 1.f : a.scale_log2;
+    const float sc = (biased || tabled) ? 1.f : a.scale_log2;
+    const float* bias_row = tabled ? a.bias_t + (size_t)(row_valid ? kvh * G + g : 0) * a.opt.bias_rows : nullptr;
 
     // stage Q: rows = (token, head) pairs, swizzled K-major; invalid rows are zero.  All
     // loads of a thread are issued before the first store (one round trip, not one each).
@@ -276,7 +283,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
-      const int key_base = (kt_begin + it) * TILE;
+      const int key_base = tile_of(it) * TILE;
       if (!mbar_wait(bar(5), it & 1, abort_flag, a.error, 15)) { ok = false; break; }
       tc_fence_after();
       const bool masked_tile = key_base + TILE - 1 > p_first || key_base < k_min ||
@@ -299,6 +306,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
         for (int j = 0; j < 64; ++j) sv[j] = fmaf(sv[j], a.scale_log2, fmaf(slope_log2, (float)j, at0));
       }
+      if (tabled) {
+        // the bias of every score by its distance; beyond the table's last row that row's
+        const int d0 = pr - (key_base + half * 64), last = a.opt.bias_rows - 1;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int d = d0 - j;
+          const float b = __ldg(bias_row + (d < 0 ? 0 : (d < last ? d : last)));
+          sv[j] = fmaf(b, LOG2E, sv[j] * a.scale_log2);
+        }
+      }
       if (masked_tile) {
         // columns of this thread's 64 keys the row may see: [lo, hi]
         const int col0 = key_base + half * 64;
@@ -306,7 +323,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int lo = (a.window > 0 ? pr - a.window + 1 : 0) - col0;
 #pragma unroll
         for (int j = 0; j < 64; ++j)
-          if (j < lo || j > hi) sv[j] = -INFINITY;
+          if ((j < lo && col0 + j >= keep) || j > hi) sv[j] = -INFINITY;
       }
       float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
@@ -373,8 +390,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           // the copies of this V tile must have landed first: they bring whole pages
           if (!mbar_wait(bar(9 + s), (it >> 1) & 1, abort_flag, a.error, 19)) { ok = false; break; }
           if (key_base + TILE - 1 > p_last) zero_rows(p_last + 1 - key_base, TILE);
-          // pages wholly before the window of the first row were not copied either
-          if (key_base < k_min) zero_rows(0, ((k_min - key_base) / ps) * ps);
+          // pages wholly before the window of the first row (and behind the kept first keys)
+          // were not copied either
+          if (key_base < k_min) {
+            const int z0 = keep > key_base ? min(TILE, ((keep - key_base + ps - 1) / ps) * ps) : 0;
+            const int z1 = min(TILE, ((k_min - key_base) / ps) * ps);
+            if (z1 > z0) zero_rows(z0, z1);
+          }
         }
       }
       tc_fence_before();
@@ -413,8 +435,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (half == 1) l_run += l_exchange[m];
     if (ok && row_valid && !*abort_flag) {
       // the factor on every value of the row: 1 / l_run without a sink or a gate
-      const float inv = attn_finish(1.f, m_ref, l_run, a.opt.sink, attn_gate_factor(a.opt, tok0 + tl, kvh * G + g));
-      __nv_bfloat16* dst = a.out + ((size_t)(tok0 + tl) * a.nh + (kvh * G + g)) * HD + half * OWN;
+      const int h = kvh * G + g;
+      const float inv = attn_finish(1.f, m_ref, l_run, a.opt.sink,
+                                    a.opt.gate_wide ? 1.f : attn_gate_factor(a.opt, tok0 + tl, h),
+                                    attn_sink_log2(a.opt, h));
+      if (a.opt.gate != nullptr && a.opt.gate_wide) {
+        // a gate per output value
+#pragma unroll
+        for (int j = 0; j < OWN; ++j) o_reg[j] *= attn_gate_factor(a.opt, tok0 + tl, h, half * OWN + j, HD);
+      }
+      __nv_bfloat16* dst = a.out + ((size_t)(tok0 + tl) * a.nh + h) * HD + half * OWN;
 #pragma unroll
       for (int j = 0; j < OWN; j += 8) {
         uint32_t w[4];
@@ -464,14 +494,19 @@ int launch_tc(const AttnArgs& a, const void* k_pages, const void* v_pages, long 
 // q_tiles: (request, first local token) for tiles of 128 / (nh / nkv) tokens.  Needs hd in
 // {64, 128}, a group size that divides 128, and a page size that is a multiple of 8 and
 // divides 128.  num_pages: pages in k_pages / v_pages ([pages, nkv, page_size, hd]).
+// bias_table_t: the bias by distance as float [nh, bias_rows] (the transpose of what the
+// other attention kernels take).
 HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, const void* k_pages,
                                       const void* v_pages, long long num_pages, const int* block_table,
                                       int bt_stride, const int* q_tiles, int n_tiles, const int* cu_tokens,
                                       const int* start_pos, int nh, int nkv, int hd, int page_size, int window,
                                       float scale, int* error, const float* slopes, int sink,
-                                      const void* gate, int gate_stride, cudaStream_t stream) {
+                                      const void* gate, int gate_stride, const float* bias_table_t,
+                                      int bias_rows, const float* sink_values, int keep_first, int gate_wide,
+                                      cudaStream_t stream) {
   if (n_tiles <= 0) return HB_OK;
   if (nkv <= 0 || nh % nkv != 0 || error == nullptr) return HB_BAD_ARGUMENT;
+  if (keep_first < 0 || (bias_table_t != nullptr && bias_rows <= 0)) return HB_BAD_ARGUMENT;
   const int G = nh / nkv;
   if (G > TILE) return HB_BAD_ARGUMENT;
   if (page_size < 8 || page_size % 8 != 0 || TILE % page_size != 0) return HB_BAD_ARGUMENT;
@@ -482,7 +517,9 @@ HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, co
   a.block_table = block_table; a.bt_stride = bt_stride; a.q_tiles = q_tiles; a.cu_tokens = cu_tokens;
   a.start_pos = start_pos; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
   a.scale_log2 = scale * LOG2E; a.error = error;
-  a.opt.slopes = slopes; a.opt.sink = sink; a.opt.gate = (const __nv_bfloat16*)gate; a.opt.gate_stride = gate_stride;
+  a.opt = AttnOptions{slopes, (const __nv_bfloat16*)gate, gate_stride, sink, nullptr, bias_rows, sink_values,
+                      window > 0 ? keep_first : 0, gate_wide};
+  a.bias_t = bias_table_t;
   const long long rows = num_pages * nkv * page_size;
   if (hd == 128) return launch_tc<128>(a, k_pages, v_pages, rows, n_tiles, stream);
   if (hd == 64) return launch_tc<64>(a, k_pages, v_pages, rows, n_tiles, stream);

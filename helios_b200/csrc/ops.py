@@ -114,13 +114,12 @@ def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
 
 def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
                                value_dim: int, tiled: bool = True):
-    """Libraries attention with ``AttentionOptions`` may choose from at these sizes (``tiled``:
-    whether the options are ones the tcgen05 kernel takes too)."""
+    """Libraries attention with ``AttentionOptions`` may choose from at these sizes."""
     if dtype != torch.bfloat16 or head_dim not in TILED_HEAD_DIMS or value_dim != head_dim \
             or not ATTENTION_OPTIONS_TILED:
         return ("attention_generic",)
     names = ["attention_bf16"]
-    if tiled and ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
+    if ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
         names.append("attention_tc")
     return tuple(names)
 
@@ -299,7 +298,9 @@ class AttentionOptions:
 
     ``slopes``   float32 [heads]: score - slopes[h] * (query position - key position)
     ``bias_table`` float32 [rows, heads]: score + bias_table[min(distance, rows - 1), h]
-                 (``distance_bias_rows`` makes one from a table of buckets)
+                 (``distance_bias_rows`` makes one from a table of buckets); ``bias_table_t``,
+                 its transpose as a contiguous tensor, is what the tcgen05 kernel reads (made at
+                 the call where it is not given)
     ``sink``     the softmax has a key that carries no value: weights
                  exp(s_j) / (exp(sink) + sum_j exp(s_j)); its score is 0, or
                  ``sink_values[h]`` (float32 [heads]) where given
@@ -312,12 +313,14 @@ class AttentionOptions:
     ``value_dim`` values per head where they differ from the keys' (None: the same)"""
 
     __slots__ = ("slopes", "sink", "gate", "gate_stride", "value_dim", "bias_table", "sink_values",
-                 "keep_first", "gate_wide")
+                 "keep_first", "gate_wide", "bias_table_t")
 
     def __init__(self, slopes: Optional[torch.Tensor] = None, sink: bool = False,
                  gate: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
                  bias_table: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None,
-                 keep_first: int = 0, gate_wide: bool = False) -> None:
+                 keep_first: int = 0, gate_wide: bool = False,
+                 bias_table_t: Optional[torch.Tensor] = None) -> None:
+        self.bias_table_t = bias_table_t
         self.slopes, self.sink, self.gate, self.value_dim = slopes, bool(sink) or sink_values is not None, gate, value_dim
         self.bias_table, self.sink_values = bias_table, sink_values
         self.keep_first, self.gate_wide = int(keep_first or 0), bool(gate_wide)
@@ -330,14 +333,8 @@ class AttentionOptions:
 
     @property
     def tiled(self) -> bool:
-        """Whether the tcgen05 prefill kernel takes these options."""
-        return self.value_dim is None and self.bias_table is None and self.sink_values is None \
-            and not self.keep_first and not self.gate_wide
-
-    @property
-    def tiled_mma(self) -> bool:
-        """Whether the ``mma.sync`` kernels (split-context decode, tiled prefill) take these
-        options: all of them, as long as values have the keys' size."""
+        """Whether the tensor-core kernels (split-context decode, tcgen05 and ``mma.sync``
+        prefill) take these options: all of them, as long as values have the keys' size."""
         return self.value_dim is None
 
     def check(self, tokens: int, num_heads: int, like: torch.Tensor, value_dim: int = 0) -> None:
@@ -395,16 +392,12 @@ _NO_OPTIONS = AttentionOptions()
 
 
 def _tiled_options(options: Optional[AttentionOptions], tokens: int, num_heads: int,
-                   like: torch.Tensor, head_dim: int = 0, mma: bool = False) -> AttentionOptions:
-    """Checked options for the tensor-core kernels, whose values have the keys' size (``mma``:
-    for the ``mma.sync`` kernels, which take every other option)."""
+                   like: torch.Tensor, head_dim: int = 0) -> AttentionOptions:
+    """Checked options for the tensor-core kernels, whose values have the keys' size."""
     if options is None:
         return _NO_OPTIONS
     if options.value_dim is not None:
         raise KernelError("the tensor-core attention kernels take values of the keys' size only")
-    if not (options.tiled_mma if mma else options.tiled):
-        raise KernelError("this tensor-core attention kernel takes no bias table, sink values, kept first "
-                          "keys or gate per value")
     options.check(tokens, num_heads, like, head_dim)
     return options
 
@@ -1057,7 +1050,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     S = qkv.shape[0]
     if block_table.shape[0] != S or positions.numel() != S:
         raise KernelError("decode attention needs one token per request")
-    opt = _tiled_options(options, S, num_heads, qkv, head_dim, mma=True)
+    opt = _tiled_options(options, S, num_heads, qkv, head_dim)
     cos = sin = None
     if rotary is not None and rotary[0] is not None:
         cos, sin = rotary
@@ -1143,7 +1136,7 @@ def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: to
                           f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
     heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
     T = qkv.shape[0]
-    opt = _tiled_options(options, T, num_heads, qkv, head_dim, mma=True)
+    opt = _tiled_options(options, T, num_heads, qkv, head_dim)
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_prefill_bf16",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -1201,12 +1194,22 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _stream()),
              "attention_prefill_pair")
         return out
-    opt = _tiled_options(options, T, num_heads, qkv)
-    f = _fn("attention_tc", "hb_attention_prefill_tc", common + [c_void_p, c_int, c_void_p, c_int, c_void_p])
+    opt = _tiled_options(options, T, num_heads, qkv, head_dim)
+    bias_t = opt.bias_table_t
+    if opt.bias_table is not None and bias_t is None:
+        bias_t = opt.bias_table.t().contiguous()
+    if bias_t is not None:
+        _check(bias_t, "bias_table_t", torch.float32, 2)
+        if opt.bias_table is None or tuple(bias_t.shape) != (num_heads, opt.bias_table.shape[0]):
+            raise KernelError(f"the transposed bias table {tuple(bias_t.shape)} does not fit")
+    f = _fn("attention_tc", "hb_attention_prefill_tc",
+            common + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
            block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos), num_heads,
            num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _p(opt.slopes),
-           int(opt.sink), _p(opt.gate), opt.gate_stride, _stream()),
+           int(opt.sink), _p(opt.gate), opt.gate_stride, _p(bias_t),
+           0 if bias_t is None else int(bias_t.shape[1]), _p(opt.sink_values), opt.keep_first if window else 0,
+           1 if opt.gate_wide else 0, _stream()),
          "attention_prefill_tc")
     return out
 
@@ -1323,7 +1326,7 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
     for portions, the ``mma.sync`` kernel for the sizes that one does not take.  Everything
     else, and float32, runs one warp a (token, head)."""
     tiled = (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
-             and options.tiled_mma)
+             and options.tiled)
     decode = tiled and ctx.decode_only and num_heads // num_kv_heads <= 16
     fused = None
     if isinstance(prepare, RotateNormPrepare):
@@ -1350,7 +1353,7 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
                                          None, fused is not None,
                                          decode_warps(ctx.num_seqs * num_kv_heads, splits, head_dim,
                                                       ctx.max_context_len), options=options, qk_norm=fused)
-        if (ATTENTION_TCGEN05 and options.tiled and ctx.max_tokens_per_seq >= 16
+        if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)
             return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,

@@ -190,7 +190,7 @@ class SinkGQAAttention(Mixer):
         self.qk_bias, self.out_bias = bool(qk_bias), bool(out_bias)
         self.rel_name, self.sink_name, self.bias_suffix = rel_name, sink_name, bias_suffix
         self.w_in = self.b_in = self.w_o = self.b_o = self.q_weight = self.k_weight = self.slopes = None
-        self.bias_rows = self.sink_values = None
+        self.bias_rows = self.bias_rows_t = self.sink_values = None
         q, kv = num_heads * head_dim, num_kv_heads * head_dim
         self._value_col = q + kv if values == "projected" else None
         self._gate_col = q + kv + (num_kv_heads * value_dim if values == "projected" else 0)
@@ -199,8 +199,7 @@ class SinkGQAAttention(Mixer):
         self._rotate_prepare = values == "keys" or position is not None or qk_norm == "plain"
         if self._rotate_prepare and self.q_temperature is not None:
             raise ValueError("a query temperature goes with weighted q/k norms and projected values only")
-        self._tiled_options = not (distance_table is not None or sink == "learned" or self.keep_first
-                                   or head_gate == "wide" or value_dim != head_dim)
+        self._tiled_options = value_dim == head_dim
 
     # ---------------------------------------------------------------- what it keeps
     def cache_spec(self) -> PagedCacheSpec:
@@ -264,6 +263,7 @@ class SinkGQAAttention(Mixer):
             self.slopes = torch.tensor(self.slope_values, dtype=torch.float32, device=self.w_o.device)
         if self.distance_table is not None:
             self.bias_rows = ops.distance_bias_rows(tensors[self.rel_name], self.distance_table[1], self.window)
+            self.bias_rows_t = self.bias_rows.t().contiguous()      # what the tcgen05 kernel reads
         if self.sink == "learned":
             self.sink_values = tensors[self.sink_name].contiguous()
 
@@ -272,7 +272,8 @@ class SinkGQAAttention(Mixer):
         return ops.AttentionOptions(slopes=self.slopes, sink=bool(self.sink), gate=gate,
                                     value_dim=None if self.value_dim == self.head_dim else self.value_dim,
                                     bias_table=self.bias_rows, sink_values=self.sink_values,
-                                    keep_first=self.keep_first, gate_wide=self.head_gate == "wide")
+                                    keep_first=self.keep_first, gate_wide=self.head_gate == "wide",
+                                    bias_table_t=self.bias_rows_t)
 
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
         rows = ops.linear(x, self.w_in, self.b_in)

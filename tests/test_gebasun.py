@@ -393,10 +393,11 @@ def _attend(ops, q, kp, vp, order, q_pos, nh, nkv, hd, page, scale, window, opti
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("decode", [True, False])
+@pytest.mark.parametrize("decode", [True, False, "early"])
 @pytest.mark.parametrize("dtype,hd,page", [("float32", 40, 16), ("bfloat16", 64, 16), ("bfloat16", 32, 16),
                                            ("bfloat16", 96, 16), ("bfloat16", 48, 16), ("bfloat16", 128, 24),
-                                           ("bfloat16", 64, 8), ("bfloat16", 96, 32)])
+                                           ("bfloat16", 64, 8), ("bfloat16", 96, 32), ("bfloat16", 128, 16),
+                                           ("bfloat16", 128, 32)])
 def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
     """One request of 300 tokens in scrambled pages of 16 (or 8, 24, 32), a window of 37 and 21 kept first
     tokens, a bias table, learned sinks and a gate per value.  Every query is aligned with ONE
@@ -404,7 +405,9 @@ def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
     bias: the oldest key inside the window and the one just outside, the last kept token and
     the first that is not, keys at page borders, position 0, the query's own.  A key that is
     NOT visible must leave no trace.  Then queries against which every key scores far below
-    the sink.  Every row also against the plain softmax.  Single tokens in bfloat16 also with
+    the sink.  Every row also against the plain softmax.  Portions at positions 230-299 (the kept
+    tokens in a tile of their own) and 40-109 (kept tokens and window in one tile); heads of 64
+    and 128 with pages that divide 128 run on the tcgen05 kernel.  Single tokens in bfloat16 also with
     the context cut into 1, 3, 5 and 12 slices (the kept tokens then fall into a slice of their
     own, share one with the window, or are all there is)."""
     from helios_b200.csrc import ops
@@ -419,7 +422,7 @@ def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
     kp, vp, order = _paged(keys, values, page, g, dt)
     rel = torch.randn(rows, nh, generator=g)
     sink = torch.tensor([0.5, -1.0, 2.0, 0.0])
-    if decode:
+    if decode is True:
         # (query position, chosen key, visible)
         cases = [(299, 263, True), (299, 262, False), (299, 20, True), (299, 21, False), (299, 0, True),
                  (299, 15, True), (299, 16, True), (299, 299, True), (299, 288, True), (299, 287, True),
@@ -429,9 +432,17 @@ def test_attention_singles_out_keys_at_every_edge(dtype, hd, page, decode):
         q_pos = torch.tensor([c[0] for c in cases] + [299, 40, 0], dtype=torch.int32)
         chosen = [c[1:] for c in cases] + [None] * 3
     else:
-        q_pos = torch.arange(230, 300, dtype=torch.int32)
-        picks = {0: 194, 1: 194, 2: 20, 3: 21, 4: 0, 5: 15, 6: 16, 10: 240, 20: 214, 21: 214, 40: 255, 41: 256,
-                 60: 254, 69: 263, 68: 261}
+        if decode == "early":
+            # a portion whose window still reaches the kept tokens: they and the window's keys share
+            # a tile, with keys between them that nobody sees
+            q_pos = torch.arange(40, 110, dtype=torch.int32)
+            picks = {0: 3, 1: 4, 2: 5, 5: 21, 17: 20, 18: 21, 19: 22, 30: 21, 31: 20, 32: 0, 40: 44, 41: 44, 42: 45,
+                     60: 0, 61: 64, 62: 63, 69: 109, 68: 72}
+            decode = False
+        else:
+            q_pos = torch.arange(230, 300, dtype=torch.int32)
+            picks = {0: 194, 1: 194, 2: 20, 3: 21, 4: 0, 5: 15, 6: 16, 10: 240, 20: 214, 21: 214, 40: 255, 41: 256,
+                     60: 254, 69: 263, 68: 261}
         chosen = []
         for r, p in enumerate(q_pos.tolist()):
             j = picks.get(r)
