@@ -6,8 +6,8 @@
 //   S <- a S + dt B x^T        (S is [N, P])
 //   y  = S^T C + D x
 //
-// The columns of S never mix: a quad of threads owns one column (a quarter of its N rows
-// each, in registers) and walks the request's tokens in order from the state the request's
+// The columns of S never mix: a group of 4 or 8 threads owns one column (a share of its N
+// rows each, in registers) and walks the request's tokens in order from the state the request's
 // slot holds, so a request's numbers do not depend on how its tokens were cut into steps or
 // on the rest of the batch.  State, step sizes, decays and the recurrence are float32.
 //
@@ -18,21 +18,21 @@
 #include "common.cuh"
 
 constexpr int SSM_CHUNK = 16;       // tokens staged in shared memory at a time
-constexpr int SSM_COLS = 32;        // columns of S a block owns (a quad of threads each)
+constexpr int SSM_COLS = 32;        // columns of S a block owns (PARTS threads each)
 
-// One token of one column.  The quad's thread `part` owns the rows 4 (part + 4 k) + e of the
-// column (k < ROWS / 4, e < 4): groups of four consecutive rows, dealt round the quad, so that
-// the four threads read 64 consecutive bytes of B and of C.  Bj and Cj hold 4 ROWS floats
-// (zeros beyond the state's rows, which keeps those entries of s at zero).  Both scan kernels
-// go through here, so a token's numbers do not depend on which of them ran.
-template <int ROWS>
+// One token of one column.  PARTS (4 or 8) neighbouring threads share a column: thread `part`
+// owns the rows 4 (part + PARTS k) + e (k < ROWS / 4, e < 4): groups of four consecutive rows,
+// dealt round the threads, so that they read consecutive 16-byte pieces of B and of C.  Bj and
+// Cj hold PARTS x ROWS floats (zeros beyond the state's rows, which keeps those entries of s at
+// zero).  Both scan kernels go through here, so a token's numbers do not depend on which ran.
+template <int ROWS, int PARTS>
 __device__ __forceinline__ float ssm_token(float (&s)[ROWS], const float* __restrict__ Bj,
                                            const float* __restrict__ Cj, float a, float dx, int part) {
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int k = 0; k < ROWS / 4; ++k) {
-    const float4 b = *reinterpret_cast<const float4*>(Bj + 4 * (part + 4 * k));
-    const float4 c = *reinterpret_cast<const float4*>(Cj + 4 * (part + 4 * k));
+    const float4 b = *reinterpret_cast<const float4*>(Bj + 4 * (part + PARTS * k));
+    const float4 c = *reinterpret_cast<const float4*>(Cj + 4 * (part + PARTS * k));
     s[4 * k + 0] = fmaf(a, s[4 * k + 0], dx * b.x);
     s[4 * k + 1] = fmaf(a, s[4 * k + 1], dx * b.y);
     s[4 * k + 2] = fmaf(a, s[4 * k + 2], dx * b.z);
@@ -45,18 +45,20 @@ __device__ __forceinline__ float ssm_token(float (&s)[ROWS], const float* __rest
   float r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
   r += __shfl_xor_sync(0xffffffffu, r, 1);
   r += __shfl_xor_sync(0xffffffffu, r, 2);
+  if (PARTS == 8) r += __shfl_xor_sync(0xffffffffu, r, 4);
   return r;
 }
 
-__device__ __forceinline__ int ssm_row(int part, int i) { return 4 * (part + 4 * (i >> 2)) + (i & 3); }
+template <int PARTS>
+__device__ __forceinline__ int ssm_row(int part, int i) { return 4 * (part + PARTS * (i >> 2)) + (i & 3); }
 
 __device__ __forceinline__ float ssm_softplus(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
 // Steps of few tokens a request (decoding): inputs are read where the convolution left them.
 // xbc [T, ld]: x at x_off + h * P, B at b_off + g * N, C at c_off + g * N (after the short
 // convolution and silu); dt_raw [T, dt_ld] at column h.  state of a slot: [heads, N, P].
-template <typename T, int ROWS>
-__global__ void __launch_bounds__(SSM_COLS * 4)
+template <typename T, int ROWS, int PARTS>
+__global__ void __launch_bounds__(SSM_COLS * PARTS)
 ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_off, int b_off, int c_off,
                 const T* __restrict__ dt_raw, int dt_ld, const float* __restrict__ a_log,
                 const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
@@ -64,7 +66,7 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
                 const int* __restrict__ slots, int heads, int groups, int N, int P) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int NP = 4 * ROWS;
+  constexpr int NP = PARTS * ROWS;
   extern __shared__ __align__(16) float sm[];
   float* Bs = sm;                              // [SSM_CHUNK][NP]
   float* Cs = Bs + SSM_CHUNK * NP;             // [SSM_CHUNK][NP]
@@ -74,7 +76,7 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
   const int h = blockIdx.y, seq = blockIdx.z;
   const int g = h / (heads / groups);
   const int col0 = blockIdx.x * SSM_COLS;
-  const int quad = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int quad = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
   const int col = col0 + quad;
   const bool live = col < P;
   const int t0 = cu_tokens[seq], t1 = cu_tokens[seq + 1];
@@ -82,7 +84,7 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
   float s[ROWS];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int n = ssm_row(part, i);
+    const int n = ssm_row<PARTS>(part, i);
     s[i] = (live && n < N) ? S[(size_t)n * P + col] : 0.f;
   }
   const float neg_rate = -expf(a_log[h]);
@@ -108,20 +110,20 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
     __syncthreads();
     for (int j = 0; j < n_tok; ++j) {
       const float xv = xs[j * SSM_COLS + quad];
-      const float acc = ssm_token<ROWS>(s, Bs + j * NP, Cs + j * NP, as[j], dts[j] * xv, part);
+      const float acc = ssm_token<ROWS, PARTS>(s, Bs + j * NP, Cs + j * NP, as[j], dts[j] * xv, part);
       if (live && part == 0) y[(size_t)(c0 + j) * heads * P + (size_t)h * P + col] = fmaf(skip, xv, acc);
     }
   }
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int n = ssm_row(part, i);
+    const int n = ssm_row<PARTS>(part, i);
     if (live && n < N) S[(size_t)n * P + col] = s[i];
   }
 }
 
 // Steps with portions of prompts.  `ssm_stage` (parallel over tokens) first lays the scan's
 // inputs out as float32 rows that copy in 16-byte pieces whatever the sizes:
-//   bc [T, groups, 2 NP]   B then C, NP = 4 ROWS floats each, zeros beyond N
+//   bc [T, groups, 2 NP]   B then C, NP = PARTS x ROWS floats each, zeros beyond N
 //   xs [T, heads, PP]      x, PP = P rounded up to whole blocks of SSM_COLS columns, zeros beyond P
 //   da [T, heads, 2]       dt = softplus(dt_raw + dt_bias) and the decay exp(-exp(A_log) dt)
 template <typename T>
@@ -162,20 +164,20 @@ __device__ __forceinline__ void ssm_cp8(void* smem, const void* gmem) {
 
 // The scan over staged rows: chunks of SSM_CHUNK tokens arrive by cp.async one chunk ahead of
 // the one being computed; a chunk's outputs leave through shared memory as whole rows.
-template <int ROWS>
-__global__ void __launch_bounds__(SSM_COLS * 4)
+template <int ROWS, int PARTS>
+__global__ void __launch_bounds__(SSM_COLS * PARTS)
 ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, const float* __restrict__ xst,
                        const float* __restrict__ da, const float* __restrict__ d_skip,
                        float* __restrict__ state, long state_stride, const int* __restrict__ cu_tokens,
                        const int* __restrict__ slots, int heads, int groups, int N, int P, int PP) {
-  constexpr int NP = 4 * ROWS;
+  constexpr int NP = PARTS * ROWS;
   constexpr int STAGE = SSM_CHUNK * (2 * NP + SSM_COLS + 2);     // floats a stage
   extern __shared__ __align__(16) float sm[];
   float* ys = sm + 2 * STAGE;                  // [SSM_CHUNK][SSM_COLS]
   const int h = blockIdx.y, seq = blockIdx.z;
   const int g = h / (heads / groups);
   const int col0 = blockIdx.x * SSM_COLS;
-  const int quad = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int quad = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
   const int col = col0 + quad;
   const bool live = col < P;
   const int t0 = cu_tokens[seq], t1 = cu_tokens[seq + 1];
@@ -183,7 +185,7 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
   float s[ROWS];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int n = ssm_row(part, i);
+    const int n = ssm_row<PARTS>(part, i);
     s[i] = (live && n < N) ? S[(size_t)n * P + col] : 0.f;
   }
   const float skip = d_skip[h];
@@ -215,11 +217,19 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
     const float* bcs = sm + stage * STAGE;
     const float* xs = bcs + SSM_CHUNK * 2 * NP;
     const float* das = xs + SSM_CHUNK * SSM_COLS;
-    for (int j = 0; j < n_tok; ++j) {
+    auto token = [&](int j) {
       const float xv = xs[j * SSM_COLS + quad];
       const float2 d = *reinterpret_cast<const float2*>(das + 2 * j);
-      const float acc = ssm_token<ROWS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part);
+      const float acc = ssm_token<ROWS, PARTS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part);
       if (part == 0) ys[j * SSM_COLS + quad] = fmaf(skip, xv, acc);
+    };
+    if (n_tok == SSM_CHUNK) {
+      // whole chunks unrolled: only the state's update chains one token to the next, so the
+      // loads, the read-out's sums and their shuffles of neighbouring tokens overlap
+#pragma unroll 4
+      for (int j = 0; j < SSM_CHUNK; ++j) token(j);
+    } else {
+      for (int j = 0; j < n_tok; ++j) token(j);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n_tok * SSM_COLS; i += blockDim.x) {
@@ -230,12 +240,14 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
   asm volatile("cp.async.wait_group 0;\n" ::);
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
-    const int n = ssm_row(part, i);
+    const int n = ssm_row<PARTS>(part, i);
     if (live && n < N) S[(size_t)n * P + col] = s[i];
   }
 }
 
-static inline int ssm_rows_for(int N) { return N <= 16 ? 4 : N <= 32 ? 8 : N <= 64 ? 16 : N <= 128 ? 32 : 64; }
+// Floats a padded row of B or C takes: PARTS x ROWS, with 4 threads a column up to 32 state
+// rows and 8 beyond (more warps an SM to hide the loads of B and C, fewer rows a thread).
+static inline int ssm_padded_rows(int N) { return N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256; }
 
 HB_EXPORT int hb_ssm_scan(float* y, const void* xbc, int ld, int x_off, int b_off, int c_off,
                           const void* dt_raw, int dt_ld, const float* a_log, const float* dt_bias,
@@ -244,19 +256,19 @@ HB_EXPORT int hb_ssm_scan(float* y, const void* xbc, int ld, int x_off, int b_of
                           int act_dt, cudaStream_t stream) {
   if (n_tokens <= 0 || n_seqs <= 0) return HB_OK;
   if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || N > 256 || P <= 0) return HB_BAD_ARGUMENT;
-  const int NP = 4 * ssm_rows_for(N);
+  const int NP = ssm_padded_rows(N);
   const size_t smem = (size_t)(2 * SSM_CHUNK * NP + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK) * sizeof(float);
   const dim3 grid((P + SSM_COLS - 1) / SSM_COLS, heads, n_seqs);
-#define HB_SSM(R)                                                                                   \
-  hb_launch(ssm_scan_kernel<TA, R>, grid, dim3(SSM_COLS * 4), smem, stream, y, (const TA*)xbc, ld,  \
-            x_off, b_off, c_off, (const TA*)dt_raw, dt_ld, a_log, dt_bias, d_skip, state,           \
+#define HB_SSM(R, PT)                                                                               \
+  hb_launch(ssm_scan_kernel<TA, R, PT>, grid, dim3(SSM_COLS * PT), smem, stream, y, (const TA*)xbc, \
+            ld, x_off, b_off, c_off, (const TA*)dt_raw, dt_ld, a_log, dt_bias, d_skip, state,       \
             state_stride, cu_tokens, slots, heads, groups, N, P)
   HB_DISPATCH_DTYPE(act_dt, TA,
-    if (N <= 16) HB_SSM(4);
-    else if (N <= 32) HB_SSM(8);
-    else if (N <= 64) HB_SSM(16);
-    else if (N <= 128) HB_SSM(32);
-    else HB_SSM(64));
+    if (NP == 16) HB_SSM(4, 4);
+    else if (NP == 32) HB_SSM(8, 4);
+    else if (NP == 64) HB_SSM(8, 8);
+    else if (NP == 128) HB_SSM(16, 8);
+    else HB_SSM(32, 8));
 #undef HB_SSM
   return hb_check_launch();
 }
@@ -264,28 +276,28 @@ HB_EXPORT int hb_ssm_scan(float* y, const void* xbc, int ld, int x_off, int b_of
 // Floats the staged rows of a token take: bc, xs, da (see ssm_stage_kernel).
 HB_EXPORT int hb_ssm_stage_sizes(int heads, int groups, int N, int P, int* bc, int* xs, int* da) {
   if (heads <= 0 || groups <= 0 || N <= 0 || N > 256 || P <= 0) return HB_BAD_ARGUMENT;
-  *bc = groups * 2 * 4 * ssm_rows_for(N);
+  *bc = groups * 2 * ssm_padded_rows(N);
   *xs = heads * ((P + SSM_COLS - 1) / SSM_COLS) * SSM_COLS;
   *da = heads * 2;
   return HB_OK;
 }
 
-template <int ROWS>
+template <int ROWS, int PARTS>
 static int ssm_launch_staged(float* y, const float* bc, const float* xs, const float* da, const float* d_skip,
                              float* state, long state_stride, const int* cu_tokens, const int* slots,
                              int n_seqs, int heads, int groups, int N, int P, int PP, cudaStream_t stream) {
-  constexpr int NP = 4 * ROWS;
+  constexpr int NP = PARTS * ROWS;
   const size_t smem = (size_t)(2 * SSM_CHUNK * (2 * NP + SSM_COLS + 2) + SSM_CHUNK * SSM_COLS) * sizeof(float);
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
-    if (cudaFuncSetAttribute(ssm_scan_staged_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ssm_scan_staged_kernel<ROWS, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return HB_LAUNCH_FAILED;
     raised = true;
   }
   // a plain launch: started while the kernel before it still fills the SMs, the scan's few
   // long-lived blocks would share SMs with it for their whole life
-  ssm_scan_staged_kernel<ROWS><<<dim3(PP / SSM_COLS, heads, n_seqs), dim3(SSM_COLS * 4), smem, stream>>>(
+  ssm_scan_staged_kernel<ROWS, PARTS><<<dim3(PP / SSM_COLS, heads, n_seqs), dim3(SSM_COLS * PARTS), smem, stream>>>(
       y, bc, xs, da, d_skip, state, state_stride, cu_tokens, slots, heads, groups, N, P, PP);
   return hb_check_launch();
 }
@@ -299,20 +311,20 @@ HB_EXPORT int hb_ssm_scan_staged(float* y, float* bc, float* xs, float* da, cons
                                  int groups, int N, int P, int act_dt, cudaStream_t stream) {
   if (n_tokens <= 0 || n_seqs <= 0) return HB_OK;
   if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || N > 256 || P <= 0) return HB_BAD_ARGUMENT;
-  const int rows = ssm_rows_for(N), NP = 4 * rows;
+  const int NP = ssm_padded_rows(N);
   const int PP = (P + SSM_COLS - 1) / SSM_COLS * SSM_COLS;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(ssm_stage_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, bc, xs, da, (const TA*)xbc, ld,
               x_off, b_off, c_off, (const TA*)dt_raw, dt_ld, a_log, dt_bias, heads, groups, N, P, NP, PP));
   const int st = hb_check_launch();
   if (st != HB_OK) return st;
-#define HB_SSM(R) return ssm_launch_staged<R>(y, bc, xs, da, d_skip, state, state_stride, cu_tokens, slots, \
-                                              n_seqs, heads, groups, N, P, PP, stream)
-  if (rows == 4) HB_SSM(4);
-  if (rows == 8) HB_SSM(8);
-  if (rows == 16) HB_SSM(16);
-  if (rows == 32) HB_SSM(32);
-  HB_SSM(64);
+#define HB_SSM(R, PT) return ssm_launch_staged<R, PT>(y, bc, xs, da, d_skip, state, state_stride, cu_tokens, \
+                                                      slots, n_seqs, heads, groups, N, P, PP, stream)
+  if (NP == 16) HB_SSM(4, 4);
+  if (NP == 32) HB_SSM(8, 4);
+  if (NP == 64) HB_SSM(8, 8);
+  if (NP == 128) HB_SSM(16, 8);
+  HB_SSM(32, 8);
 #undef HB_SSM
 }
 
