@@ -7,8 +7,9 @@
 //   y  = S^T C + D x
 //
 // The columns of S never mix: a group of 4 or 8 threads owns one column (a share of its N
-// rows each, in registers) and walks the request's tokens in order from the state the request's
-// slot holds, so a request's numbers do not depend on how its tokens were cut into steps or
+// rows each, in registers; neighbouring lanes in the kernel for portions, the same lane of 4 or
+// 8 warps in the kernel for single tokens) and walks the request's tokens in order from the
+// state the request's slot holds, so a request's numbers do not depend on how its tokens were cut into steps or
 // on the rest of the batch.  State, step sizes, decays and the recurrence are float32.
 //
 // Kernels: `ssm_scan` (the recurrence, for steps of few tokens a request), `ssm_stage` +
@@ -20,13 +21,13 @@
 constexpr int SSM_CHUNK = 16;       // tokens staged in shared memory at a time
 constexpr int SSM_COLS = 32;        // columns of S a block owns (PARTS threads each)
 
-// One token of one column.  PARTS (4 or 8) neighbouring threads share a column: thread `part`
+// One thread's share of one token of one column.  PARTS (4 or 8) threads share a column: thread `part`
 // owns the rows 4 (part + PARTS k) + e (k < ROWS / 4, e < 4): groups of four consecutive rows,
 // dealt round the threads, so that they read consecutive 16-byte pieces of B and of C.  Bj and
 // Cj hold PARTS x ROWS floats (zeros beyond the state's rows, which keeps those entries of s at
 // zero).  Both scan kernels go through here, so a token's numbers do not depend on which ran.
 template <int ROWS, int PARTS>
-__device__ __forceinline__ float ssm_token(float (&s)[ROWS], const float* __restrict__ Bj,
+__device__ __forceinline__ float ssm_token_share(float (&s)[ROWS], const float* __restrict__ Bj,
                                            const float* __restrict__ Cj, float a, float dx, int part) {
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -42,11 +43,25 @@ __device__ __forceinline__ float ssm_token(float (&s)[ROWS], const float* __rest
     acc[2] = fmaf(s[4 * k + 2], c.z, acc[2]);
     acc[3] = fmaf(s[4 * k + 3], c.w, acc[3]);
   }
-  float r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
+
+// The read-out of a column is the sum of its threads' shares in the order of a butterfly:
+// ((r0 + r1) + (r2 + r3)) + ((r4 + r5) + (r6 + r7)).  The kernel for portions has the shares in
+// neighbouring lanes, the kernel for single tokens in shared memory; both add in this order.
+template <int PARTS>
+__device__ __forceinline__ float ssm_sum_lanes(float r) {
   r += __shfl_xor_sync(0xffffffffu, r, 1);
   r += __shfl_xor_sync(0xffffffffu, r, 2);
   if (PARTS == 8) r += __shfl_xor_sync(0xffffffffu, r, 4);
   return r;
+}
+
+template <int PARTS>
+__device__ __forceinline__ float ssm_sum_shared(const float* __restrict__ r, int stride) {
+  float lo = (r[0] + r[stride]) + (r[2 * stride] + r[3 * stride]);
+  if (PARTS == 8) lo += (r[4 * stride] + r[5 * stride]) + (r[6 * stride] + r[7 * stride]);
+  return lo;
 }
 
 template <int PARTS>
@@ -58,7 +73,7 @@ __device__ __forceinline__ float ssm_softplus(float v) { return fmaxf(v, 0.f) + 
 // xbc [T, ld]: x at x_off + h * P, B at b_off + g * N, C at c_off + g * N (after the short
 // convolution and silu); dt_raw [T, dt_ld] at column h.  state of a slot: [heads, N, P].
 template <typename T, int ROWS, int PARTS>
-__global__ void __launch_bounds__(SSM_COLS * PARTS)
+__global__ void __launch_bounds__(SSM_COLS * PARTS, ROWS <= 8 ? 1024 / (SSM_COLS * PARTS) : ROWS <= 16 ? 3 : 1)
 ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_off, int b_off, int c_off,
                 const T* __restrict__ dt_raw, int dt_ld, const float* __restrict__ a_log,
                 const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
@@ -73,10 +88,13 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
   float* xs = Cs + SSM_CHUNK * NP;             // [SSM_CHUNK][SSM_COLS]
   float* dts = xs + SSM_CHUNK * SSM_COLS;      // [SSM_CHUNK]
   float* as = dts + SSM_CHUNK;                 // [SSM_CHUNK]
+  float* shares = as + SSM_CHUNK;              // [2][PARTS][SSM_COLS]: the tokens take turns
   const int h = blockIdx.y, seq = blockIdx.z;
   const int g = h / (heads / groups);
   const int col0 = blockIdx.x * SSM_COLS;
-  const int quad = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
+  // a lane a column, a warp a share of the rows: the state, which is most of what a step of
+  // single tokens moves, is read and written as whole rows of 32 columns
+  const int quad = threadIdx.x & 31, part = threadIdx.x >> 5;
   const int col = col0 + quad;
   const bool live = col < P;
   const int t0 = cu_tokens[seq], t1 = cu_tokens[seq + 1];
@@ -87,6 +105,7 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
     const int n = ssm_row<PARTS>(part, i);
     s[i] = (live && n < N) ? S[(size_t)n * P + col] : 0.f;
   }
+  int turn = 0;
   const float neg_rate = -expf(a_log[h]);
   const float bias = dt_bias[h], skip = d_skip[h];
   for (int c0 = t0; c0 < t1; c0 += SSM_CHUNK) {
@@ -110,8 +129,12 @@ ssm_scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, int ld, int x_
     __syncthreads();
     for (int j = 0; j < n_tok; ++j) {
       const float xv = xs[j * SSM_COLS + quad];
-      const float acc = ssm_token<ROWS, PARTS>(s, Bs + j * NP, Cs + j * NP, as[j], dts[j] * xv, part);
-      if (live && part == 0) y[(size_t)(c0 + j) * heads * P + (size_t)h * P + col] = fmaf(skip, xv, acc);
+      float* mine = shares + turn * PARTS * SSM_COLS;
+      mine[part * SSM_COLS + quad] = ssm_token_share<ROWS, PARTS>(s, Bs + j * NP, Cs + j * NP, as[j], dts[j] * xv, part);
+      __syncthreads();
+      if (live && part == 0)
+        y[(size_t)(c0 + j) * heads * P + (size_t)h * P + col] = fmaf(skip, xv, ssm_sum_shared<PARTS>(mine + quad, SSM_COLS));
+      turn ^= 1;
     }
   }
 #pragma unroll
@@ -220,7 +243,7 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
     auto token = [&](int j) {
       const float xv = xs[j * SSM_COLS + quad];
       const float2 d = *reinterpret_cast<const float2*>(das + 2 * j);
-      const float acc = ssm_token<ROWS, PARTS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part);
+      const float acc = ssm_sum_lanes<PARTS>(ssm_token_share<ROWS, PARTS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part));
       if (part == 0) ys[j * SSM_COLS + quad] = fmaf(skip, xv, acc);
     };
     if (n_tok == SSM_CHUNK) {
@@ -257,7 +280,7 @@ HB_EXPORT int hb_ssm_scan(float* y, const void* xbc, int ld, int x_off, int b_of
   if (n_tokens <= 0 || n_seqs <= 0) return HB_OK;
   if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || N > 256 || P <= 0) return HB_BAD_ARGUMENT;
   const int NP = ssm_padded_rows(N);
-  const size_t smem = (size_t)(2 * SSM_CHUNK * NP + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK) * sizeof(float);
+  const size_t smem = (size_t)(2 * SSM_CHUNK * NP + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK + 2 * 8 * SSM_COLS) * sizeof(float);
   const dim3 grid((P + SSM_COLS - 1) / SSM_COLS, heads, n_seqs);
 #define HB_SSM(R, PT)                                                                               \
   hb_launch(ssm_scan_kernel<TA, R, PT>, grid, dim3(SSM_COLS * PT), smem, stream, y, (const TA*)xbc, \
