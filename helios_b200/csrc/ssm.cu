@@ -186,20 +186,21 @@ __device__ __forceinline__ void ssm_cp8(void* smem, const void* gmem) {
 }
 
 // The scan over staged rows: chunks of SSM_CHUNK tokens arrive by cp.async one chunk ahead of
-// the one being computed; a chunk's outputs leave through shared memory as whole rows.
-template <int ROWS, int PARTS>
-__global__ void __launch_bounds__(SSM_COLS * PARTS)
+// the one being computed; a chunk's outputs leave through shared memory as whole rows.  A block
+// owns COLS (16 or 32) columns; a column's numbers do not depend on which.
+template <int ROWS, int PARTS, int COLS>
+__global__ void __launch_bounds__(COLS * PARTS)
 ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, const float* __restrict__ xst,
                        const float* __restrict__ da, const float* __restrict__ d_skip,
                        float* __restrict__ state, long state_stride, const int* __restrict__ cu_tokens,
                        const int* __restrict__ slots, int heads, int groups, int N, int P, int PP) {
   constexpr int NP = PARTS * ROWS;
-  constexpr int STAGE = SSM_CHUNK * (2 * NP + SSM_COLS + 2);     // floats a stage
+  constexpr int STAGE = SSM_CHUNK * (2 * NP + COLS + 2);     // floats a stage
   extern __shared__ __align__(16) float sm[];
-  float* ys = sm + 2 * STAGE;                  // [SSM_CHUNK][SSM_COLS]
+  float* ys = sm + 2 * STAGE;                  // [SSM_CHUNK][COLS]
   const int h = blockIdx.y, seq = blockIdx.z;
   const int g = h / (heads / groups);
-  const int col0 = blockIdx.x * SSM_COLS;
+  const int col0 = blockIdx.x * COLS;
   const int quad = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
   const int col = col0 + quad;
   const bool live = col < P;
@@ -215,16 +216,16 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
   auto fetch = [&](int c0, int stage) {
     const int n_tok = min(SSM_CHUNK, t1 - c0);
     float* bcs = sm + stage * STAGE;                       // [SSM_CHUNK][2 NP]
-    float* xs = bcs + SSM_CHUNK * 2 * NP;                  // [SSM_CHUNK][SSM_COLS]
-    float* das = xs + SSM_CHUNK * SSM_COLS;                // [SSM_CHUNK][2]
-    constexpr int V_BC = 2 * NP / 4, V_X = SSM_COLS / 4;
+    float* xs = bcs + SSM_CHUNK * 2 * NP;                  // [SSM_CHUNK][COLS]
+    float* das = xs + SSM_CHUNK * COLS;                // [SSM_CHUNK][2]
+    constexpr int V_BC = 2 * NP / 4, V_X = COLS / 4;
     for (int i = threadIdx.x; i < n_tok * V_BC; i += blockDim.x) {
       const int j = i / V_BC, v = i - j * V_BC;
       ssm_cp16(bcs + j * 2 * NP + v * 4, bc + ((size_t)(c0 + j) * groups + g) * 2 * NP + v * 4);
     }
     for (int i = threadIdx.x; i < n_tok * V_X; i += blockDim.x) {
       const int j = i / V_X, v = i - j * V_X;
-      ssm_cp16(xs + j * SSM_COLS + v * 4, xst + ((size_t)(c0 + j) * heads + h) * PP + col0 + v * 4);
+      ssm_cp16(xs + j * COLS + v * 4, xst + ((size_t)(c0 + j) * heads + h) * PP + col0 + v * 4);
     }
     if (threadIdx.x < n_tok) ssm_cp8(das + threadIdx.x * 2, da + ((size_t)(c0 + threadIdx.x) * heads + h) * 2);
   };
@@ -239,24 +240,40 @@ ssm_scan_staged_kernel(float* __restrict__ y, const float* __restrict__ bc, cons
     __syncthreads();
     const float* bcs = sm + stage * STAGE;
     const float* xs = bcs + SSM_CHUNK * 2 * NP;
-    const float* das = xs + SSM_CHUNK * SSM_COLS;
-    auto token = [&](int j) {
-      const float xv = xs[j * SSM_COLS + quad];
+    const float* das = xs + SSM_CHUNK * COLS;
+    auto share = [&](int j, float& xv) {
+      xv = xs[j * COLS + quad];
       const float2 d = *reinterpret_cast<const float2*>(das + 2 * j);
-      const float acc = ssm_sum_lanes<PARTS>(ssm_token_share<ROWS, PARTS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part));
-      if (part == 0) ys[j * SSM_COLS + quad] = fmaf(skip, xv, acc);
+      return ssm_token_share<ROWS, PARTS>(s, bcs + j * 2 * NP, bcs + j * 2 * NP + NP, d.y, d.x * xv, part);
     };
     if (n_tok == SSM_CHUNK) {
-      // whole chunks unrolled: only the state's update chains one token to the next, so the
-      // loads, the read-out's sums and their shuffles of neighbouring tokens overlap
-#pragma unroll 4
-      for (int j = 0; j < SSM_CHUNK; ++j) token(j);
+      // whole chunks four tokens at a time: only the state's update chains one token to the
+      // next, so the four tokens' loads come first and their read-outs' sums and shuffles
+      // overlap; the outputs are stored after the four (a store to shared memory between two
+      // tokens would keep the next token's loads behind it)
+      constexpr int GROUP = 4;
+#pragma unroll 1
+      for (int j0 = 0; j0 < SSM_CHUNK; j0 += GROUP) {
+        float r[GROUP], xv[GROUP];
+#pragma unroll
+        for (int u = 0; u < GROUP; ++u) r[u] = share(j0 + u, xv[u]);
+#pragma unroll
+        for (int u = 0; u < GROUP; ++u) r[u] = ssm_sum_lanes<PARTS>(r[u]);
+        if (part == 0) {
+#pragma unroll
+          for (int u = 0; u < GROUP; ++u) ys[(j0 + u) * COLS + quad] = fmaf(skip, xv[u], r[u]);
+        }
+      }
     } else {
-      for (int j = 0; j < n_tok; ++j) token(j);
+      for (int j = 0; j < n_tok; ++j) {
+        float xv;
+        const float r = ssm_sum_lanes<PARTS>(share(j, xv));
+        if (part == 0) ys[j * COLS + quad] = fmaf(skip, xv, r);
+      }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n_tok * SSM_COLS; i += blockDim.x) {
-      const int j = i / SSM_COLS, c = i - j * SSM_COLS;
+    for (int i = threadIdx.x; i < n_tok * COLS; i += blockDim.x) {
+      const int j = i / COLS, c = i - j * COLS;
       if (col0 + c < P) y[(size_t)(c0 + j) * heads * P + (size_t)h * P + col0 + c] = ys[i];
     }
   }
@@ -305,24 +322,49 @@ HB_EXPORT int hb_ssm_stage_sizes(int heads, int groups, int N, int P, int* bc, i
   return HB_OK;
 }
 
-template <int ROWS, int PARTS>
-static int ssm_launch_staged(float* y, const float* bc, const float* xs, const float* da, const float* d_skip,
+template <int ROWS, int PARTS, int COLS>
+static int ssm_launch_staged_cols(float* y, const float* bc, const float* xs, const float* da, const float* d_skip,
                              float* state, long state_stride, const int* cu_tokens, const int* slots,
                              int n_seqs, int heads, int groups, int N, int P, int PP, cudaStream_t stream) {
   constexpr int NP = PARTS * ROWS;
-  const size_t smem = (size_t)(2 * SSM_CHUNK * (2 * NP + SSM_COLS + 2) + SSM_CHUNK * SSM_COLS) * sizeof(float);
+  const size_t smem = (size_t)(2 * SSM_CHUNK * (2 * NP + COLS + 2) + SSM_CHUNK * COLS) * sizeof(float);
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
-    if (cudaFuncSetAttribute(ssm_scan_staged_kernel<ROWS, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ssm_scan_staged_kernel<ROWS, PARTS, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return HB_LAUNCH_FAILED;
     raised = true;
   }
   // a plain launch: started while the kernel before it still fills the SMs, the scan's few
   // long-lived blocks would share SMs with it for their whole life
-  ssm_scan_staged_kernel<ROWS, PARTS><<<dim3(PP / SSM_COLS, heads, n_seqs), dim3(SSM_COLS * PARTS), smem, stream>>>(
+  ssm_scan_staged_kernel<ROWS, PARTS, COLS><<<dim3(PP / COLS, heads, n_seqs), dim3(COLS * PARTS), smem, stream>>>(
       y, bc, xs, da, d_skip, state, state_stride, cu_tokens, slots, heads, groups, N, P, PP);
   return hb_check_launch();
+}
+
+static int ssm_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      v = 148;
+    n = v;
+  }
+  return n;
+}
+
+// Blocks of 32 columns, or of 16 where those would leave SMs without a block (one long prompt):
+// the scan's time is its tokens times a warp's time a token, whatever a block's width.
+template <int ROWS, int PARTS>
+static int ssm_launch_staged(float* y, const float* bc, const float* xs, const float* da, const float* d_skip,
+                             float* state, long state_stride, const int* cu_tokens, const int* slots,
+                             int n_seqs, int heads, int groups, int N, int P, int PP, cudaStream_t stream) {
+  if ((long)(PP / SSM_COLS) * heads * n_seqs < ssm_sm_count())
+    return ssm_launch_staged_cols<ROWS, PARTS, SSM_COLS / 2>(y, bc, xs, da, d_skip, state, state_stride, cu_tokens,
+                                                             slots, n_seqs, heads, groups, N, P, PP, stream);
+  return ssm_launch_staged_cols<ROWS, PARTS, SSM_COLS>(y, bc, xs, da, d_skip, state, state_stride, cu_tokens,
+                                                       slots, n_seqs, heads, groups, N, P, PP, stream);
 }
 
 // The scan for steps with portions of prompts: stage (into bc / xs / da, float32 buffers of
