@@ -64,8 +64,8 @@ GB_B = _model(150, 80, 3e-6, [
 ])
 # heads of 64, more kept tokens than a page, all experts chosen, one group, two taps
 GB_C = _model(180, 128, 1e-5, [
-    (_att2(8, 2, 64, 0.125, 40, 20, 32, 250000.0), _moe(48, 4, 4, 16)),
-    (_att(8, 4, 64, 0.11, 30, 32, 120), _moe(48, 4, 4, 16)),
+    (_att2(8, 2, 64, 0.125, 44, 19, 32, 300000.0), _moe(48, 4, 4, 16)),
+    (_att(8, 4, 64, 0.11, 30, 32, 110), _moe(48, 4, 4, 16)),
     (_ssm(8, 32, 64, 1, 2, 4), _moe(48, 4, 4, 16)),
 ])
 # a width that is no multiple of 8, heads of 10, a window of one page, a single tap
