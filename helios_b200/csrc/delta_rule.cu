@@ -49,6 +49,99 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
   }
 }
 
+// The same for bfloat16 rows that come in 16-byte pieces (channels, row stride and addresses
+// multiples of eight values) and 2 to 4 taps: a thread takes eight neighbouring channels of
+// CONV_TOKENS consecutive tokens, so that the channels' weights (16-byte loads) and the rows
+// the tokens share are read once; each channel's sum in the order of the kernel above.
+constexpr int CONV_TOKENS = 4;
+
+template <int TAPS>
+__global__ void __launch_bounds__(128)
+causal_conv_silu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                               int ld, const float* __restrict__ w, const float* __restrict__ bias,
+                               const float* __restrict__ state, long state_stride,
+                               const int* __restrict__ seq_of_token,
+                               const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                               int n_tokens, int channels) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int ROWS = CONV_TOKENS + TAPS - 1;
+  const int pieces = channels / 8;
+  const int groups = (n_tokens + CONV_TOKENS - 1) / CONV_TOKENS;
+  const size_t total = (size_t)groups * pieces;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const int tg = (int)(idx / pieces), c = (int)(idx - (size_t)tg * pieces) * 8;
+    const int t0 = tg * CONV_TOKENS;
+    // the eight channels' weights are 8 x TAPS consecutive floats from a 32-byte boundary
+    float wr[8 * TAPS];
+#pragma unroll
+    for (int i = 0; i < 2 * TAPS; ++i) {
+      const float4 q = *reinterpret_cast<const float4*>(w + (size_t)c * TAPS + 4 * i);
+      wr[4 * i] = q.x; wr[4 * i + 1] = q.y; wr[4 * i + 2] = q.z; wr[4 * i + 3] = q.w;
+    }
+    float b8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) b8[e] = bias ? bias[c + e] : 0.f;
+    // rows t0 - (TAPS - 1) .. t0 + CONV_TOKENS - 1 of the step, where they exist
+    float v[ROWS][8];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = t0 - (TAPS - 1) + r;
+      if (row >= 0 && row < n_tokens) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)row * ld + c);
+        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[e]));
+          v[r][2 * e] = f.x;
+          v[r][2 * e + 1] = f.y;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[r][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < CONV_TOKENS; ++u) {
+      const int t = t0 + u;
+      if (t >= n_tokens) break;
+      const int s = seq_of_token[t];
+      const int local = t - cu_tokens[s];
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = b8[e];
+      if (local >= TAPS - 1) {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(wr[e * TAPS + j], v[u + j][e], acc[e]);
+        }
+      } else {
+        // the request's first tokens of this step: the inputs before them are in its slot
+        const float* st = state + (size_t)slots[s] * state_stride + (size_t)c * (TAPS - 1);
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+          const int src = local - (TAPS - 1) + j;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float in = src >= 0 ? v[u + j][e] : st[(size_t)e * (TAPS - 1) + (TAPS - 1) + src];
+            acc[e] = fmaf(wr[e * TAPS + j], in, acc[e]);
+          }
+        }
+      }
+      uint32_t res[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 o = __floats2bfloat162_rn(acc[2 * e] / (1.f + expf(-acc[2 * e])),
+                                                       acc[2 * e + 1] / (1.f + expf(-acc[2 * e + 1])));
+        res[e] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+      *reinterpret_cast<uint4*>(out + (size_t)t * channels + c) = make_uint4(res[0], res[1], res[2], res[3]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void causal_conv_state_kernel(float* __restrict__ state, long state_stride,
                                          const T* __restrict__ x, int ld,
@@ -80,12 +173,27 @@ HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float*
   if (n_tokens <= 0 || channels <= 0) return HB_OK;
   if (taps < 1 || ld < channels) return HB_BAD_ARGUMENT;
   const size_t total = (size_t)n_tokens * channels;
-  size_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  HB_DISPATCH_DTYPE(act_dt, TA,
-    hb_launch(causal_conv_silu_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out,
-              (const TA*)x, ld, w, bias, (const float*)state, state_stride, seq_of_token, cu_tokens, slots,
-              n_tokens, channels, taps));
+  // steps of few tokens keep a thread a (token, channel): more threads, shorter chains of loads
+  if (act_dt == HB_BF16 && n_tokens >= 64 && channels % 8 == 0 && ld % 8 == 0 && taps >= 2 && taps <= 4 &&
+      ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
+    size_t vblocks = ((size_t)((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS) * (channels / 8) + 127) / 128;
+    if (vblocks > 148 * 32) vblocks = 148 * 32;
+#define HB_CONV8(TP)                                                                                          \
+    hb_launch(causal_conv_silu_bf16x8_kernel<TP>, dim3((unsigned)vblocks), dim3(128), 0, stream,              \
+              (__nv_bfloat16*)out, (const __nv_bfloat16*)x, ld, w, bias, (const float*)state, state_stride,   \
+              seq_of_token, cu_tokens, slots, n_tokens, channels)
+    if (taps == 2) HB_CONV8(2);
+    else if (taps == 3) HB_CONV8(3);
+    else HB_CONV8(4);
+#undef HB_CONV8
+  } else {
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    HB_DISPATCH_DTYPE(act_dt, TA,
+      hb_launch(causal_conv_silu_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out,
+                (const TA*)x, ld, w, bias, (const float*)state, state_stride, seq_of_token, cu_tokens, slots,
+                n_tokens, channels, taps));
+  }
   if (taps > 1) {
     const size_t total2 = (size_t)n_seqs * channels;
     size_t blocks2 = (total2 + 255) / 256;

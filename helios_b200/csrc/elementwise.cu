@@ -1129,11 +1129,48 @@ __global__ void unary_act_kernel(T* __restrict__ out, const T* __restrict__ x, c
   }
 }
 
+// bfloat16 rows whose values come in 16-byte pieces: eight values a thread and step.
+__global__ void unary_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                                        size_t pieces, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < pieces;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[idx];
+    const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t res[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[e]));
+      float y[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const float u = k ? v.y : v.x;
+        if (kind == ACT_RELU2) { const float r = fmaxf(u, 0.f); y[k] = r * r; }
+        else if (kind == ACT_SILU) y[k] = u / (1.f + expf(-u));
+        else y[k] = 0.5f * u * (1.f + tanhf(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+      }
+      const __nv_bfloat162 o = __floats2bfloat162_rn(y[0], y[1]);
+      res[e] = *reinterpret_cast<const uint32_t*>(&o);
+    }
+    reinterpret_cast<uint4*>(out)[idx] = make_uint4(res[0], res[1], res[2], res[3]);
+  }
+}
+
 HB_EXPORT int hb_unary_act(void* out, const void* x, const void* gate, int gate_ld, int T, int W, int kind,
                            int act_dt, cudaStream_t stream) {
   if (T <= 0 || W <= 0) return HB_OK;
   if (kind < 0 || kind > 3 || (kind == ACT_SIGMOID_GATE && gate == nullptr)) return HB_BAD_ARGUMENT;
   const size_t total = (size_t)T * W;
+  if (act_dt == HB_BF16 && kind != ACT_SIGMOID_GATE && total % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+    const size_t pieces = total / 8;
+    size_t vblocks = (pieces + 255) / 256;
+    if (vblocks > 148 * 16) vblocks = 148 * 16;
+    hb_launch(unary_act_bf16x8_kernel, dim3((unsigned)vblocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
+              (const __nv_bfloat16*)x, pieces, kind);
+    return hb_check_launch();
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   HB_DISPATCH_DTYPE(act_dt, TA,

@@ -558,25 +558,33 @@ def test_gate_before_a_norm_in_parts_and_the_short_convolution(dtype):
         v = y.double() * pg.silu(z[:, 4:64].double())
         want = pg.rms_unit(v.view(9, parts, 60 // parts), 1e-5).reshape(9, 60) * w.double()
         assert (got - want).abs().max() < (1e-5 if dtype == "float32" else 3e-2)
-    # the convolution: two requests, the second continues from inputs its slot holds
-    C, taps = 11, 4
-    x = torch.randn(12, 20, generator=g).to(dt)
-    cw, cb = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
-    state = torch.zeros(3, C * (taps - 1)).cuda()
-    ctx = SimpleNamespace(seq_of_token=torch.tensor([0] * 5 + [1] * 2, dtype=torch.int32).cuda(),
-                          cu_tokens=torch.tensor([0, 5, 7], dtype=torch.int32).cuda(),
-                          slots=torch.tensor([2, 0], dtype=torch.int32).cuda(), num_seqs=2)
-    first = ops.causal_conv_silu(ctx, x[:7].cuda(), C, cw.cuda(), state, bias=cb.cuda(), col0=6).float().cpu()
-    ctx2 = SimpleNamespace(seq_of_token=torch.tensor([0] * 5, dtype=torch.int32).cuda(),
-                           cu_tokens=torch.tensor([0, 5], dtype=torch.int32).cuda(),
-                           slots=torch.tensor([0], dtype=torch.int32).cuda(), num_seqs=1)
-    second = ops.causal_conv_silu(ctx2, x[7:].cuda(), C, cw.cuda(), state, bias=cb.cuda(), col0=6).float().cpu()
-    xa = x[:5, 6:6 + C].double()
-    xb = torch.cat([x[5:7, 6:6 + C], x[7:, 6:6 + C]]).double()
-    tol = 1e-5 if dtype == "float32" else 3e-2
-    assert (first[:5].double() - pg.silu(pg.causal_conv(xa, cw.double(), cb.double()))).abs().max() < tol
-    wb = pg.silu(pg.causal_conv(xb, cw.double(), cb.double()))
-    assert (first[5:].double() - wb[:2]).abs().max() < tol and (second.double() - wb[2:]).abs().max() < tol
+    # the convolution: two requests, the second continues from inputs its slot holds; rows of
+    # odd sizes with few tokens, and rows that come in 16-byte pieces with many (in bfloat16 a
+    # thread then takes eight channels of four tokens, across the border of the two requests)
+    for C, width, col0, taps, n0, n1, n2 in [(11, 20, 6, 4, 5, 2, 5), (16, 32, 8, 4, 81, 30, 70),
+                                             (24, 40, 16, 3, 62, 3, 66), (8, 16, 8, 2, 1, 70, 64)]:
+        x = torch.randn(n0 + n1 + n2, width, generator=g).to(dt)
+        cw, cb = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
+        state = torch.zeros(3, C * (taps - 1)).cuda()
+        ctx = SimpleNamespace(seq_of_token=torch.tensor([0] * n0 + [1] * n1, dtype=torch.int32).cuda(),
+                              cu_tokens=torch.tensor([0, n0, n0 + n1], dtype=torch.int32).cuda(),
+                              slots=torch.tensor([2, 0], dtype=torch.int32).cuda(), num_seqs=2)
+        first = ops.causal_conv_silu(ctx, x[:n0 + n1].cuda(), C, cw.cuda(), state, bias=cb.cuda(), col0=col0).float().cpu()
+        ctx2 = SimpleNamespace(seq_of_token=torch.tensor([0] * n2, dtype=torch.int32).cuda(),
+                               cu_tokens=torch.tensor([0, n2], dtype=torch.int32).cuda(),
+                               slots=torch.tensor([0], dtype=torch.int32).cuda(), num_seqs=1)
+        second = ops.causal_conv_silu(ctx2, x[n0 + n1:].cuda(), C, cw.cuda(), state, bias=cb.cuda(), col0=col0).float().cpu()
+        xa = x[:n0, col0:col0 + C].double()
+        xb = x[n0:, col0:col0 + C].double()
+        tol = 1e-5 if dtype == "float32" else 3e-2
+        assert (first[:n0].double() - pg.silu(pg.causal_conv(xa, cw.double(), cb.double()))).abs().max() < tol
+        wb = pg.silu(pg.causal_conv(xb, cw.double(), cb.double()))
+        assert (first[n0:].double() - wb[:n1]).abs().max() < tol and (second.double() - wb[n1:]).abs().max() < tol
+    # an activation of one argument, odd sizes and whole 16-byte pieces
+    for rows, cols in [(5, 7), (6, 40)]:
+        u = torch.randn(rows, cols, generator=g).to(dt)
+        got = ops.unary_act(u.cuda(), "relu2").float().cpu().double()
+        assert (got - torch.relu(u.double()) ** 2).abs().max() < (1e-6 if dtype == "float32" else 5e-2)
 
 
 @pytest.mark.gpu
