@@ -186,7 +186,7 @@ def test_configuration_is_read_layer_by_layer_and_faults_name_the_key():
     assert cfg.layers[1].mixer.keep_first == 0 and cfg.layers[1].mlp is None
     assert cfg.layers[2].mixer.bias_rows == 9 and cfg.layers[2].mixer.bias_max == 50.0
     assert cfg.layers[0].mlp.shared_ff is None and cfg.layers[0].mlp.top == 1
-    assert GebasunConfig.from_json(GB_C).layers[0].mixer.keep_first == 20
+    assert GebasunConfig.from_json(GB_C).layers[0].mixer.keep_first == 19
     for path, value, word in [(("layers", 0, "mixer", "state"), None, "state"),
                               (("layers", 1, "mixer", "rot", "dims"), 7, "dims"),
                               (("layers", 2, "mixer", "vdim"), 8, "vdim"),
