@@ -7,10 +7,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] (f32) = table[ids[t], :]      python/helios/exec/model.py:486
+// out[t, :] (f32) = table[ids[t], :] * scale      python/helios/exec/model.py:486
+// (scale: a constant some designs put on the embedded tokens; 1 for none; the product is float32)
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int H, int V) {
+                                 const int* __restrict__ ids, int H, int V, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -18,12 +19,12 @@ __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ 
   if (id < 0 || id >= V) id = 0;  // ids are validated on the host
   const T* row = table + (size_t)id * H;
   float* o = out + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 // bfloat16 table, rows of whole 16-byte chunks: 8 values per thread and trip
 __global__ void embedding_bf16x8_kernel(float* __restrict__ out, const __nv_bfloat16* __restrict__ table,
-                                        const int* __restrict__ ids, int H, int V) {
+                                        const int* __restrict__ ids, int H, int V, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -34,20 +35,23 @@ __global__ void embedding_bf16x8_kernel(float* __restrict__ out, const __nv_bflo
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
     const uint4 x = row[i];
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&x);
-    o[2 * i] = make_float4(__low2float(p[0]), __high2float(p[0]), __low2float(p[1]), __high2float(p[1]));
-    o[2 * i + 1] = make_float4(__low2float(p[2]), __high2float(p[2]), __low2float(p[3]), __high2float(p[3]));
+    o[2 * i] = make_float4(__low2float(p[0]) * scale, __high2float(p[0]) * scale, __low2float(p[1]) * scale,
+                           __high2float(p[1]) * scale);
+    o[2 * i + 1] = make_float4(__low2float(p[2]) * scale, __high2float(p[2]) * scale, __low2float(p[3]) * scale,
+                               __high2float(p[3]) * scale);
   }
 }
 
 HB_EXPORT int hb_embedding(float* out, const void* table, const int* ids, int T, int H, int V,
-                           int table_dt, cudaStream_t stream) {
+                           int table_dt, float scale, cudaStream_t stream) {
   if (T <= 0) return HB_OK;
   if (table_dt == HB_BF16 && H % 8 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0) {
-    hb_launch(embedding_bf16x8_kernel, dim3(T), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V);
+    hb_launch(embedding_bf16x8_kernel, dim3(T), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V,
+              scale);
     return hb_check_launch();
   }
   HB_DISPATCH_DTYPE(table_dt, TT,
-    hb_launch(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, out, (const TT*)table, ids, H, V));
+    hb_launch(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, out, (const TT*)table, ids, H, V, scale));
   return hb_check_launch();
 }
 
@@ -993,32 +997,33 @@ HB_EXPORT int hb_qk_norm_kv_write(void* rows, int ld, const int* positions, cons
 // rows: [T, ld] with q heads (nh * hd) from column 0, then k heads (nkv * hd); value heads
 // (nkv * vd) at column v_col, or, with v_col < 0, the values ARE the keys as projected (before
 // rotation and norm; vd = hd).  One warp per (token, head):
-//   a q or k head is rotated on its first `rot` values (value i paired with value i + rot/2,
-//   (u, v) -> (u cos - v sin, v cos + u sin), cos/sin [T, rot/2] float32; rot 0: none), then,
-//   with `norm`, divided by its root mean square over hd (eps inside the root) and multiplied
-//   by a weight per channel (wq / wk, null: none);
+//   a q or k head is rotated on its first `rot` values ((u, v) -> (u cos - v sin, v cos + u sin),
+//   cos/sin [T, rot/2] float32; rot 0: none; `pairing` QKR_HALVES: value i paired with value
+//   i + rot/2, QKR_NEIGHBOURS: value 2i with value 2i + 1), then, with `norm` QKR_NORM_HEAD,
+//   divided by its root mean square over hd (eps inside the root) and multiplied by a weight per
+//   channel (wq / wk [hd], null: none);
+//   with `norm` QKR_NORM_ROW the norm comes BEFORE the rotation and runs over the whole q row
+//   (nh * hd values) and the whole k row (nkv * hd) at once, with weights wq [nh * hd] and
+//   wk [nkv * hd]: one block a token takes the two sums first and then walks the heads;
 //   q is written back in place; k goes to the token's place in the key pages, the values to
 //   the value pages (pages: [page, kv head, slot, hd] and [.., vd]).
 // All arithmetic float32.  Without `write_cache` k is written back in place and no value moves.
 constexpr int QKR_WARPS = 4;
+constexpr int QKR_ROW_WARPS = 8;
 constexpr int QKR_MAX_HD = 256;
+enum { QKR_HALVES = 0, QKR_NEIGHBOURS = 1 };
+enum { QKR_NORM_NONE = 0, QKR_NORM_HEAD = 1, QKR_NORM_ROW = 2 };
 
+// head h of token t by one warp; `xs`: hd floats of shared memory of the warp's own.
+// row_f: QKR_NORM_ROW: 1 / rms of the head's whole row (q or k); else unused.
 template <typename T>
-__global__ void __launch_bounds__(QKR_WARPS * 32)
-qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
-                            const float* __restrict__ sin_tab, int rot, const int* __restrict__ positions,
-                            const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-                            int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens,
-                            int nh, int nkv, int hd, int vd, int norm, const float* __restrict__ wq,
-                            const float* __restrict__ wk, float eps, int page_size, int write_cache) {
-  pdl_launch_dependents();
-  pdl_wait();
-  __shared__ float head_sm[QKR_WARPS][QKR_MAX_HD];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per_token = nh + nkv + (v_col >= 0 ? nkv : 0);
-  const long item = (long)blockIdx.x * QKR_WARPS + warp;
-  if (item >= (long)n_tokens * per_token) return;
-  const int t = (int)(item / per_token), h = (int)(item - (long)t * per_token);
+__device__ __forceinline__ void
+qkr_head(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
+         const float* __restrict__ sin_tab, int rot, int pairing, const int* __restrict__ positions,
+         const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
+         T* __restrict__ k_pages, T* __restrict__ v_pages, int nh, int nkv, int hd, int vd, int norm,
+         const float* __restrict__ wq, const float* __restrict__ wk, float eps, int page_size,
+         int write_cache, int t, int h, float* xs, int lane, float row_f) {
   const int pos = positions[t];
   T* row = rows + (size_t)t * ld;
   size_t page_base = 0;
@@ -1038,13 +1043,18 @@ qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float
   }
   const bool is_q = h < nh;
   T* x = row + (size_t)h * hd;
-  float* xs = head_sm[warp];
+  const float* w = is_q ? wq : wk;
+  // the norm over the whole row: its factor and the channel's weight go on before the rotation
+  const float* w_pre = (norm == QKR_NORM_ROW && w) ? w + (size_t)(is_q ? h : h - nh) * hd : nullptr;
+  const float f_pre = norm == QKR_NORM_ROW ? row_f : 1.f;
   if (!is_q && write_cache && v_col < 0) {   // the values are the keys as projected
     T* dst = v_pages + ((page_base + (h - nh)) * page_size + slot) * vd;
     for (int d = lane; d < hd; d += 32) { const T v = x[d]; dst[d] = v; xs[d] = to_float(v); }
   } else {
     for (int d = lane; d < hd; d += 32) xs[d] = to_float(x[d]);
   }
+  if (norm == QKR_NORM_ROW)
+    for (int d = lane; d < hd; d += 32) xs[d] = xs[d] * f_pre * (w_pre ? w_pre[d] : 1.f);
   __syncwarp();
   const int half = rot >> 1;
   const float* cr = cos_tab ? cos_tab + (size_t)t * half : nullptr;
@@ -1059,17 +1069,21 @@ qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float
     if (d < hd) {
       v = xs[d];
       if (d < rot) {
-        const int j = d < half ? d : d - half;
-        const float c = cr[j], s = sr[j];
-        v = d < half ? v * c - xs[d + half] * s : v * c + xs[d - half] * s;
+        if (pairing == QKR_NEIGHBOURS) {
+          const float c = cr[d >> 1], s = sr[d >> 1];
+          v = (d & 1) ? v * c + xs[d - 1] * s : v * c - xs[d + 1] * s;
+        } else {
+          const int j = d < half ? d : d - half;
+          const float c = cr[j], s = sr[j];
+          v = d < half ? v * c - xs[d + half] * s : v * c + xs[d - half] * s;
+        }
       }
     }
     y[i] = v;
     ss = fmaf(v, v, ss);
   }
   float f = 1.f;
-  if (norm) f = rsqrtf(warp_sum(ss) / (float)hd + eps);
-  const float* w = is_q ? wq : wk;
+  if (norm == QKR_NORM_HEAD) f = rsqrtf(warp_sum(ss) / (float)hd + eps);
   T* dst = x;
   if (!is_q && write_cache) dst = k_pages + ((page_base + (h - nh)) * page_size + slot) * hd;
 #pragma unroll
@@ -1077,14 +1091,69 @@ qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float
     const int d = lane + 32 * i;
     if (d < hd) {
       float v = y[i] * f;
-      if (norm && w) v *= w[d];
+      if (norm == QKR_NORM_HEAD && w) v *= w[d];
       dst[d] = from_float<T>(v);
     }
   }
+  __syncwarp();                               // xs may serve the warp's next head
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QKR_WARPS * 32)
+qk_rotate_norm_write_kernel(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
+                            const float* __restrict__ sin_tab, int rot, int pairing,
+                            const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                            int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens,
+                            int nh, int nkv, int hd, int vd, int norm, const float* __restrict__ wq,
+                            const float* __restrict__ wk, float eps, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float head_sm[QKR_WARPS][QKR_MAX_HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = nh + nkv + (v_col >= 0 ? nkv : 0);
+  const long item = (long)blockIdx.x * QKR_WARPS + warp;
+  if (item >= (long)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), h = (int)(item - (long)t * per_token);
+  qkr_head<T>(rows, ld, v_col, cos_tab, sin_tab, rot, pairing, positions, seq_of_token, block_table, bt_stride,
+              k_pages, v_pages, nh, nkv, hd, vd, norm, wq, wk, eps, page_size, write_cache, t, h,
+              head_sm[warp], lane, 1.f);
+}
+
+// The norm over whole rows: one block a token.  The sums of squares of the q row and of the
+// k row are taken by all threads in an order that depends on the row alone; then every warp
+// walks heads warp, warp + QKR_ROW_WARPS, ...
+template <typename T>
+__global__ void __launch_bounds__(QKR_ROW_WARPS * 32)
+qk_rownorm_rotate_write_kernel(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
+                               const float* __restrict__ sin_tab, int rot, int pairing,
+                               const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                               const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
+                               T* __restrict__ v_pages, int nh, int nkv, int hd, int vd,
+                               const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                               int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float head_sm[QKR_ROW_WARPS][QKR_MAX_HD];
+  __shared__ float scratch[33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const T* row = rows + (size_t)t * ld;
+  const int nq = nh * hd, nk = nkv * hd;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = to_float(row[c]); sq = fmaf(v, v, sq); }
+  for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = to_float(row[nq + c]); sk = fmaf(v, v, sk); }
+  const float fq = rsqrtf(block_sum(sq, scratch) / (float)nq + eps);
+  const float fk = rsqrtf(block_sum(sk, scratch) / (float)nk + eps);
+  const int per_token = nh + nkv + (v_col >= 0 ? nkv : 0);
+  for (int h = warp; h < per_token; h += QKR_ROW_WARPS)
+    qkr_head<T>(const_cast<T*>(rows), ld, v_col, cos_tab, sin_tab, rot, pairing, positions, seq_of_token,
+                block_table, bt_stride, k_pages, v_pages, nh, nkv, hd, vd, QKR_NORM_ROW, wq, wk, eps,
+                page_size, write_cache, t, h, head_sm[warp], lane, h < nh ? fq : fk);
 }
 
 HB_EXPORT int hb_qk_rotate_norm_write(void* rows, int ld, int v_col, const float* cos_tab,
-                                      const float* sin_tab, int rot, const int* positions,
+                                      const float* sin_tab, int rot, int pairing, const int* positions,
                                       const int* seq_of_token, const int* block_table, int bt_stride,
                                       void* k_pages, void* v_pages, int T, int nh, int nkv, int hd, int vd,
                                       int norm, const float* wq, const float* wk, float eps, int page_size,
@@ -1092,12 +1161,20 @@ HB_EXPORT int hb_qk_rotate_norm_write(void* rows, int ld, int v_col, const float
   if (T <= 0) return HB_OK;
   if (nh <= 0 || nkv <= 0 || hd <= 0 || hd > QKR_MAX_HD || vd <= 0 || page_size <= 0 || rot < 0 ||
       rot > hd || rot % 2 || (rot > 0 && (cos_tab == nullptr || sin_tab == nullptr)) ||
+      (pairing != QKR_HALVES && pairing != QKR_NEIGHBOURS) || norm < QKR_NORM_NONE || norm > QKR_NORM_ROW ||
       (v_col < 0 && vd != hd) || (long)(nh + nkv) * hd > ld || (v_col >= 0 && (long)v_col + (long)nkv * vd > ld))
     return HB_BAD_ARGUMENT;
+  if (norm == QKR_NORM_ROW) {
+    HB_DISPATCH_DTYPE(act_dt, TA,
+      hb_launch(qk_rownorm_rotate_write_kernel<TA>, dim3((unsigned)T), dim3(QKR_ROW_WARPS * 32), 0, stream,
+                (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, pairing, positions, seq_of_token, block_table,
+                bt_stride, (TA*)k_pages, (TA*)v_pages, nh, nkv, hd, vd, wq, wk, eps, page_size, write_cache));
+    return hb_check_launch();
+  }
   const long items = (long)T * (nh + nkv + (v_col >= 0 ? nkv : 0));
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(qk_rotate_norm_write_kernel<TA>, dim3((unsigned)((items + QKR_WARPS - 1) / QKR_WARPS)),
-              dim3(QKR_WARPS * 32), 0, stream, (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, positions,
+              dim3(QKR_WARPS * 32), 0, stream, (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, pairing, positions,
               seq_of_token, block_table, bt_stride, (TA*)k_pages, (TA*)v_pages, T, nh, nkv, hd, vd, norm,
               wq, wk, eps, page_size, write_cache));
   return hb_check_launch();

@@ -15,73 +15,98 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- prepare
-// proj[t] = [q (heads x (nope + rot)) | latent (rank) | shared key part (rot)].
-// Rotary pairs dimension 2i with 2i + 1 (interleaved) over the first `nrot` of the `rot`
-// values; cos/sin tables are [T, nrot / 2] (any factor already in them).
+// What the rows of the projections want before attention; every piece is optional (a null
+// pointer leaves it out), one block a token:
+//   cq  [T, cq_ld]: a query latent of `q_rank` values, RMS-normed in place (weight cq_w);
+//   lat [T, lat_ld] = [latent (rank) | shared key part (rot)]: the latent RMS-normed (weight
+//       norm_w), the shared key part rotated, both stored as the token's row of `pages`
+//       (with `write_cache`; without it nothing of `lat` is used: another layer's rows serve);
+//   q   [T, q_ld] = heads x [nope | rot]: every head's rotated part rotated in place.
+// The rotation runs over the first `nrot` of the `rot` values; `pairing` 0: value i with value
+// i + nrot / 2 (halves), 1: value 2i with value 2i + 1 (neighbours); cos/sin tables are
+// [T, nrot / 2] (any factor already in them).  float32 arithmetic, eps inside the roots.
+enum { LAT_HALVES = 0, LAT_NEIGHBOURS = 1 };
+
+template <typename T>
+__device__ __forceinline__ void latent_rotate(T* __restrict__ dst, const T* __restrict__ src, int i, int half,
+                                              int pairing, const float* __restrict__ ct,
+                                              const float* __restrict__ st) {
+  const int a = pairing == LAT_NEIGHBOURS ? 2 * i : i;
+  const int b = pairing == LAT_NEIGHBOURS ? 2 * i + 1 : i + half;
+  const float u = to_float(src[a]), v = to_float(src[b]);
+  dst[a] = from_float<T>(u * ct[i] - v * st[i]);
+  dst[b] = from_float<T>(v * ct[i] + u * st[i]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(T* __restrict__ proj, int ld, T* __restrict__ pages,
-                      const float* __restrict__ norm_w, const float* __restrict__ cos_tab,
-                      const float* __restrict__ sin_tab, const int* __restrict__ positions,
-                      const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-                      int bt_stride, int heads, int nope, int rot, int rank, int nrot,
-                      int page_size, float eps, int write_cache) {
+latent_prepare_kernel(T* __restrict__ q, int q_ld, const T* __restrict__ lat_rows, int lat_ld,
+                      T* __restrict__ cq, int cq_ld, int q_rank, const float* __restrict__ cq_w,
+                      T* __restrict__ pages, const float* __restrict__ norm_w,
+                      const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ block_table, int bt_stride, int heads, int nope, int rot,
+                      int rank, int nrot, int pairing, int page_size, float eps, int write_cache) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  T* row = proj + (size_t)t * ld;
-  T* lat = row + (size_t)heads * (nope + rot);
   const int half = nrot / 2;
   const float* ct = cos_tab + (size_t)t * half;
   const float* st = sin_tab + (size_t)t * half;
-  const int pos = positions[t];
-  T* dst = nullptr;
-  if (write_cache) {
-    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
-    dst = pages + ((size_t)page * page_size + pos % page_size) * (rank + rot);
+  if (cq) {                                  // the query latent, normed in float32 in place
+    T* row = cq + (size_t)t * cq_ld;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) { const float v = to_float(row[c]); ss += v * v; }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+      row[c] = from_float<T>(to_float(row[c]) * rstd * cq_w[c]);
   }
-  // the latent, normed in float32
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < rank; c += blockDim.x) { const float v = to_float(lat[c]); ss += v * v; }
-  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)rank + eps);
-  if (dst)
+  if (lat_rows && write_cache) {
+    const T* lat = lat_rows + (size_t)t * lat_ld;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    T* dst = pages + ((size_t)page * page_size + pos % page_size) * (rank + rot);
+    // the latent, normed in float32
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) { const float v = to_float(lat[c]); ss += v * v; }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)rank + eps);
     for (int c = threadIdx.x; c < rank; c += blockDim.x)
       dst[c] = from_float<T>(to_float(lat[c]) * rstd * norm_w[c]);
-  // the shared key part: rotated pairs, the rest as it is
-  if (dst) {
+    // the shared key part: rotated pairs, the rest as it is
     const T* kr = lat + rank;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const float u = to_float(kr[2 * i]), v = to_float(kr[2 * i + 1]);
-      dst[rank + 2 * i] = from_float<T>(u * ct[i] - v * st[i]);
-      dst[rank + 2 * i + 1] = from_float<T>(v * ct[i] + u * st[i]);
-    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) latent_rotate(dst + rank, kr, i, half, pairing, ct, st);
     for (int c = nrot + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = kr[c];
   }
-  // the queries' rotated parts, in place
-  for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    T* qr = row + (size_t)h * (nope + rot) + nope;
-    const float u = to_float(qr[2 * i]), v = to_float(qr[2 * i + 1]);
-    qr[2 * i] = from_float<T>(u * ct[i] - v * st[i]);
-    qr[2 * i + 1] = from_float<T>(v * ct[i] + u * st[i]);
+  if (q) {                                   // the queries' rotated parts, in place
+    T* row = q + (size_t)t * q_ld;
+    for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+      const int h = idx / half, i = idx - h * half;
+      T* qr = row + (size_t)h * (nope + rot) + nope;
+      latent_rotate(qr, qr, i, half, pairing, ct, st);
+    }
   }
 }
 
-HB_EXPORT int hb_latent_prepare(void* proj, int ld, void* pages, const float* norm_w,
+HB_EXPORT int hb_latent_prepare(void* q, int q_ld, const void* lat, int lat_ld, void* cq, int cq_ld,
+                                int q_rank, const float* cq_w, void* pages, const float* norm_w,
                                 const float* cos_tab, const float* sin_tab, const int* positions,
                                 const int* seq_of_token, const int* block_table, int bt_stride,
-                                int T, int heads, int nope, int rot, int rank, int nrot,
+                                int T, int heads, int nope, int rot, int rank, int nrot, int pairing,
                                 int page_size, float eps, int write_cache, int act_dt,
                                 cudaStream_t stream) {
   if (T <= 0) return HB_OK;
   if (heads <= 0 || nope < 0 || rot < 0 || rank <= 0 || nrot < 0 || nrot > rot || nrot % 2 ||
-      page_size <= 0 || ld < heads * (nope + rot) + rank + rot)
+      page_size <= 0 || (pairing != LAT_HALVES && pairing != LAT_NEIGHBOURS) ||
+      (q && q_ld < heads * (nope + rot)) || (lat && lat_ld < rank + rot) ||
+      (cq && (q_rank <= 0 || cq_ld < q_rank || cq_w == nullptr)) ||
+      (lat && write_cache && (pages == nullptr || norm_w == nullptr)) ||
+      (nrot > 0 && (cos_tab == nullptr || sin_tab == nullptr)))
     return HB_BAD_ARGUMENT;
   HB_DISPATCH_DTYPE(act_dt, TA,
-    hb_launch(latent_prepare_kernel<TA>, dim3(T), dim3(128), 0, stream, (TA*)proj, ld, (TA*)pages,
-              norm_w, cos_tab, sin_tab, positions, seq_of_token, block_table, bt_stride, heads,
-              nope, rot, rank, nrot, page_size, eps, write_cache));
+    hb_launch(latent_prepare_kernel<TA>, dim3(T), dim3(128), 0, stream, (TA*)q, q_ld, (const TA*)lat, lat_ld,
+              (TA*)cq, cq_ld, q_rank, cq_w, (TA*)pages, norm_w, cos_tab, sin_tab, positions, seq_of_token,
+              block_table, bt_stride, heads, nope, rot, rank, nrot, pairing, page_size, eps, write_cache));
   return hb_check_launch();
 }
 

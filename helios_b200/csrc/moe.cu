@@ -58,7 +58,7 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
                                 const float* __restrict__ logits_in,
                                 const float* __restrict__ correction, const float* __restrict__ bias,
                                 float* __restrict__ biased, int n_tokens, int experts,
-                                int top, int kind) {
+                                int top, int kind, int normalize, float weight_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,7 +101,12 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
   if (kind == MOE_TOP_SOFTMAX) {    // the first pick holds the largest logit
     float sum = 0.f;
     for (int k = 0; k < top; ++k) { top_logit[k] = expf(top_logit[k] - top_logit[0]); sum += top_logit[k]; }
-    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = top_logit[k] / sum;
+    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = top_logit[k] / sum * weight_scale;
+  } else if (normalize || weight_scale != 1.f) {      // the chosen scores over their sum, in the picks' order
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += top_logit[k];
+    const float f = normalize ? weight_scale / (sum + 1e-20f) : weight_scale;
+    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = top_logit[k] * f;
   }
 }
 
@@ -110,14 +115,22 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
 // every pick are warp reductions (a pick: the largest choice value, the lower index on a tie).
 // The sums run over the lanes' partial sums in the order of the shuffle tree, whatever the
 // batch: a token's weights depend on its own logits alone.
+//
+// `groups` > 1: the outputs form that many equal runs of neighbours; a run scores the largest
+// choice value in it, and only the outputs of the `keep` best runs (the lower index among
+// equals) can be chosen.  `normalize`: the weights are the chosen scores over their sum
+// (+ 1e-20, added up in the picks' order); `weight_scale` multiplies every weight.
 constexpr int MOE_PER_LANE = 8;
 
 __global__ void __launch_bounds__(128)
 moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
                      const float* __restrict__ logits, const float* __restrict__ correction,
-                     const float* __restrict__ bias, int n_tokens, int experts, int top, int kind) {
+                     const float* __restrict__ bias, int n_tokens, int experts, int top, int kind,
+                     int groups, int keep, int normalize, float weight_scale) {
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float group_sm[4][32 * MOE_PER_LANE];     // a warp's choice values, then its runs' scores
+  __shared__ unsigned char kept_sm[4][32 * MOE_PER_LANE];
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
@@ -151,8 +164,59 @@ moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
     if (kind == MOE_SIGMOID) score[i] = 1.f / (1.f + expf(-logit));     // MOE_TOP_SOFTMAX keeps the logit
     choice[i] = by_logit ? logit : score[i] + ((correction && e < experts) ? correction[e] : 0.f);
   }
-  unsigned taken = 0;        // bit i: this lane's i-th output is chosen already
-  float first_logit = 0.f, top_sum = 0.f, mine = 0.f;     // MOE_TOP_SOFTMAX: lane k keeps pick k's term
+  unsigned taken = 0;        // bit i: this lane's i-th output is chosen already (or not eligible)
+  if (groups > 1) {
+    float* cv = group_sm[threadIdx.x >> 5];
+    unsigned char* kept = kept_sm[threadIdx.x >> 5];
+    const int per = experts / groups;
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts) cv[e] = choice[i];
+    }
+    __syncwarp();
+    float run[MOE_PER_LANE];             // lane l scores the runs l, l + 32, ...
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int g = lane + 32 * i;
+      float m = -INFINITY;
+      if (g < groups)
+        for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, cv[e]);     // a NaN never wins
+      run[i] = m;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups) kept[g] = 0;
+    }
+    unsigned run_taken = 0;
+    for (int k = 0; k < keep; ++k) {
+      float best = 0.f;
+      int at = -1;
+#pragma unroll
+      for (int i = 0; i < MOE_PER_LANE; ++i) {
+        const int g = lane + 32 * i;
+        if (g >= groups || (run_taken >> i & 1u)) continue;
+        if (at < 0 || run[i] > best) { best = run[i]; at = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa >= 0 && (at < 0 || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+      }
+      if (at >= 0 && (at & 31) == lane) { run_taken |= 1u << (at >> 5); kept[at] = 1; }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && !kept[e / per]) taken |= 1u << i;
+    }
+  }
+  const bool own_weights = kind == MOE_TOP_SOFTMAX || normalize;   // lane k keeps pick k's term
+  float first_logit = 0.f, top_sum = 0.f, mine = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = 0.f, best_score = 0.f;
     int at = -1;
@@ -183,31 +247,41 @@ moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
       top_sum += term;
       if (lane == k) mine = term;
       if (lane == 0) ids[(size_t)t * top + k] = at;
+    } else if (normalize) {              // the chosen scores add up in the picks' order
+      top_sum += best_score;
+      if (lane == k) mine = best_score;
+      if (lane == 0) ids[(size_t)t * top + k] = at;
     } else if (lane == 0) {
       ids[(size_t)t * top + k] = at;
-      weights[(size_t)t * top + k] = best_score;
+      weights[(size_t)t * top + k] = best_score * weight_scale;
     }
   }
-  if (kind == MOE_TOP_SOFTMAX && lane < top) weights[(size_t)t * top + lane] = mine / top_sum;
+  if (own_weights && lane < top)
+    weights[(size_t)t * top + lane] = mine / (top_sum + (kind == MOE_TOP_SOFTMAX ? 0.f : 1e-20f)) * weight_scale;
 }
 
 // `biased`: scratch [n_tokens, experts] for the logits with their bias (rows of more than
 // 32 * MOE_PER_LANE router outputs with a bias only)
+// `groups`, `keep`: see the warp kernel (rows of up to 32 * MOE_PER_LANE router outputs only)
 HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, const float* correction,
                           const float* bias, float* biased, int n_tokens, int experts, int top, int kind,
-                          cudaStream_t stream) {
+                          int groups, int keep, int normalize, float weight_scale, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP ||
       (kind != MOE_SIGMOID && kind != MOE_SOFTMAX && kind != MOE_TOP_SOFTMAX) || top > 32)
     return HB_BAD_ARGUMENT;
+  if (groups < 1 || (groups > 1 && (experts % groups || keep < 1 || keep > groups ||
+                                    top > keep * (experts / groups) || experts > 32 * MOE_PER_LANE)) ||
+      (normalize && kind == MOE_TOP_SOFTMAX))
+    return HB_BAD_ARGUMENT;
   if (experts <= 32 * MOE_PER_LANE) {
     hb_launch(moe_topk_warp_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, ids, weights,
-              logits, correction, bias, n_tokens, experts, top, kind);
+              logits, correction, bias, n_tokens, experts, top, kind, groups, keep, normalize, weight_scale);
     return hb_check_launch();
   }
   if (bias != nullptr && biased == nullptr) return HB_BAD_ARGUMENT;
   hb_launch(moe_topk_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids, weights,
-            logits, correction, bias, biased, n_tokens, experts, top, kind);
+            logits, correction, bias, biased, n_tokens, experts, top, kind, normalize, weight_scale);
   return hb_check_launch();
 }
 

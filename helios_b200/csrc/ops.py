@@ -125,15 +125,16 @@ def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads:
 
 
 # ------------------------------------------------------------------ embedding
-def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    """float32 [T, H] rows of ``table`` ([V, H], float32 or bfloat16) at int32 ``ids``."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """float32 [T, H] rows of ``table`` ([V, H], float32 or bfloat16) at int32 ``ids``, times
+    ``scale`` (a float32 product)."""
     _check(ids, "ids", torch.int32, 1)
     _check(table, "table", None, 2)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     f = _fn("elementwise", "hb_embedding",
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(table), _p(ids), T, H, V, _dt(table.dtype), _stream()), "embedding")
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _run(f(_p(out), _p(table), _p(ids), T, H, V, _dt(table.dtype), float(scale), _stream()), "embedding")
     return out
 
 
@@ -1334,7 +1335,7 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
         qk_rotate_norm_write(qkv, pr.cos, pr.sin, ctx.positions, ctx.seq_of_token, block_table, k_pages,
                              v_pages, num_heads, num_kv_heads, head_dim, options.value_dim or head_dim,
                              page_size, pr.norm, pr.q_weight, pr.k_weight, pr.eps, pr.value_col,
-                             write_cache=pr.write)
+                             write_cache=pr.write, pairing=pr.pairing)
     elif prepare is not None:
         wq, wk, eps, coef, every, write = prepare
         if decode and write and ATTENTION_DECODE_QK_NORM and qkv.is_contiguous():
@@ -1370,20 +1371,27 @@ def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, 
 
 class RotateNormPrepare:
     """What the rows of a fused projection still want before attention (``attention``'s
-    ``prepare``): a rotation of q and k by ``cos`` / ``sin`` ([T, rot/2] float32, value i of a
-    head paired with value i + rot/2; None: no rotation), then, with ``norm``, the division of
-    every q and k head by its root mean square (eps inside the root) and optional weights per
-    channel; the keys go to the key pages and the values to the value pages: from the columns
-    at ``value_col``, or, with ``value_col`` None, the values ARE the keys as projected, before
-    rotation and norm."""
+    ``prepare``): a rotation of q and k by ``cos`` / ``sin`` ([T, rot/2] float32; None: no
+    rotation; ``pairing`` "halves": value i of a head paired with value i + rot/2, "neighbours":
+    value 2i with value 2i + 1), then, with ``norm`` True, the division of every q and k head by
+    its root mean square (eps inside the root) and optional weights per channel ([head_dim]).
+    ``norm`` "row": the RMS norm comes BEFORE the rotation and runs over the whole q row and the
+    whole k row (all heads at once) with weights of the rows' sizes.  The keys go to the key
+    pages and the values to the value pages: from the columns at ``value_col``, or, with
+    ``value_col`` None, the values ARE the keys as projected, before rotation and norm."""
 
-    __slots__ = ("cos", "sin", "norm", "q_weight", "k_weight", "eps", "value_col", "write")
+    __slots__ = ("cos", "sin", "norm", "q_weight", "k_weight", "eps", "value_col", "write", "pairing")
 
-    def __init__(self, cos=None, sin=None, norm: bool = True, q_weight=None, k_weight=None,
-                 eps: float = 1e-6, value_col: Optional[int] = None, write: bool = True) -> None:
-        self.cos, self.sin, self.norm = cos, sin, bool(norm)
+    def __init__(self, cos=None, sin=None, norm=True, q_weight=None, k_weight=None,
+                 eps: float = 1e-6, value_col: Optional[int] = None, write: bool = True,
+                 pairing: str = "halves") -> None:
+        self.cos, self.sin = cos, sin
+        self.norm = norm if norm == "row" else bool(norm)
         self.q_weight, self.k_weight, self.eps = q_weight, k_weight, float(eps)
-        self.value_col, self.write = value_col, bool(write)
+        self.value_col, self.write, self.pairing = value_col, bool(write), pairing
+
+
+ROTARY_PAIRINGS = {"halves": 0, "neighbours": 1}
 
 
 def qk_rotate_norm_write(rows: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
@@ -1391,10 +1399,12 @@ def qk_rotate_norm_write(rows: torch.Tensor, cos: Optional[torch.Tensor], sin: O
                          k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], num_heads: int,
                          num_kv_heads: int, head_dim: int, value_dim: int, page_size: int, norm: bool,
                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
-                         value_col: Optional[int], write_cache: bool = True) -> None:
+                         value_col: Optional[int], write_cache: bool = True, pairing: str = "halves") -> None:
     """See ``RotateNormPrepare``: rows [T, ld] hold q heads, then k heads, from column 0; q is
     rotated and normed in place, k rotated and normed into the key pages (in place without
     ``write_cache``), the values copied into the value pages.  float32 arithmetic."""
+    if pairing not in ROTARY_PAIRINGS:
+        raise KernelError(f"pairing {pairing!r} is not one of {sorted(ROTARY_PAIRINGS)}")
     _check(rows, "rows", None, 2)
     T, ld = rows.shape
     _check(positions, "positions", torch.int32, 1)
@@ -1409,11 +1419,12 @@ def qk_rotate_norm_write(rows: torch.Tensor, cos: Optional[torch.Tensor], sin: O
         rot = 2 * cos.shape[1]
         if rot > head_dim:
             raise KernelError(f"rotary dimension {rot} exceeds head_dim {head_dim}")
-    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+    for name, w, heads in (("q_weight", q_weight, num_heads), ("k_weight", k_weight, num_kv_heads)):
         if w is not None:
             _check(w, name, torch.float32, 1)
-            if w.numel() != head_dim:
-                raise KernelError(f"{name} has {w.numel()} entries for heads of {head_dim}")
+            want = head_dim * (heads if norm == "row" else 1)
+            if w.numel() != want:
+                raise KernelError(f"{name} has {w.numel()} entries where the norm runs over {want}")
     if head_dim > 256:
         raise KernelError(f"heads of {head_dim} values are not supported (at most 256)")
     if value_col is None and value_dim != head_dim:
@@ -1425,13 +1436,14 @@ def qk_rotate_norm_write(rows: torch.Tensor, cos: Optional[torch.Tensor], sin: O
                 raise KernelError(f"{name} has shape {tuple(pages.shape)}, expected "
                                   f"[pages, {num_kv_heads}, {page_size}, {d}]")
     f = _fn("elementwise", "hb_qk_rotate_norm_write",
-            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
              c_int, c_int, c_int, c_void_p])
     _run(f(_p(rows), ld, -1 if value_col is None else int(value_col), _p(cos), _p(sin), rot,
-           _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1],
+           ROTARY_PAIRINGS[pairing], _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1],
            _p(k_pages) if write_cache else 0, _p(v_pages) if write_cache else 0, T, num_heads,
-           num_kv_heads, head_dim, value_dim, 1 if norm else 0, _p(q_weight), _p(k_weight), float(eps),
+           num_kv_heads, head_dim, value_dim, 2 if norm == "row" else (1 if norm else 0),
+           _p(q_weight), _p(k_weight), float(eps),
            page_size, 1 if write_cache else 0, _dt(rows.dtype), _stream()), "qk_rotate_norm_write")
 
 
@@ -1611,31 +1623,79 @@ def latent_prepare(proj: torch.Tensor, pages: Optional[torch.Tensor], norm_weigh
     values) and both stored as one row [rank + rot] of ``pages`` [pages, 1, page_size, rank +
     rot]; the queries' rotated parts are rotated in place."""
     _check(proj, "proj", None, 2)
-    _check(norm_weight, "norm_weight", torch.float32, 1)
+    nq = heads * (nope + rot)
+    if proj.shape[1] != nq + rank + rot:
+        raise KernelError(f"proj has {proj.shape[1]} columns, expected {nq + rank + rot}")
+    latent_prepare_parts(proj[:, :nq], proj[:, nq:], None, pages, norm_weight, None, cos, sin, positions,
+                         seq_of_token, block_table, heads, nope, rot, rank, page_size, eps,
+                         write_cache=write_cache, pairing="neighbours")
+
+
+def latent_prepare_parts(q: Optional[torch.Tensor], latent: Optional[torch.Tensor],
+                         query_latent: Optional[torch.Tensor], pages: Optional[torch.Tensor],
+                         norm_weight: Optional[torch.Tensor], query_norm_weight: Optional[torch.Tensor],
+                         cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                         seq_of_token: torch.Tensor, block_table: torch.Tensor, heads: int, nope: int,
+                         rot: int, rank: int, page_size: int, eps: float, write_cache: bool = True,
+                         pairing: str = "halves") -> None:
+    """``latent_prepare`` piece by piece; each of the three tensors is a view [T, columns] whose
+    rows may be strided (last dimension contiguous), or None to leave the piece out:
+
+    ``query_latent`` [T, q_rank]: RMS-normed in place (``query_norm_weight``);
+    ``latent`` [T, rank + rot] = [latent | shared key part]: the latent RMS-normed
+    (``norm_weight``), the shared key part rotated, both stored as the token's row of ``pages``
+    (nothing without ``write_cache``: the rows of another layer serve);
+    ``q`` [T, heads (nope + rot)]: every head's rotated part rotated in place.
+
+    ``pairing`` "halves": value i of the rotated part is paired with value i + nrot / 2,
+    "neighbours": value 2i with value 2i + 1; cos/sin are [T, nrot / 2]."""
+    like = next((x for x in (q, latent, query_latent) if x is not None), None)
+    if like is None:
+        return
+    if pairing not in ROTARY_PAIRINGS:
+        raise KernelError(f"pairing {pairing!r} is not one of {sorted(ROTARY_PAIRINGS)}")
+    T = like.shape[0]
+    for name, x, cols in (("q", q, heads * (nope + rot)), ("latent", latent, rank + rot),
+                          ("query_latent", query_latent, None)):
+        if x is None:
+            continue
+        if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.shape[0] != T or x.dtype != like.dtype \
+                or (cols is not None and x.shape[1] != cols):
+            raise KernelError(f"latent_prepare: {name} {tuple(x.shape)} does not fit ({T} rows of {cols} columns)")
     _check(cos, "cos", torch.float32, 2)
     _check(sin, "sin", torch.float32, 2)
     _check(positions, "positions", torch.int32, 1)
     _check(seq_of_token, "seq_of_token", torch.int32, 1)
     _check(block_table, "block_table", torch.int32, 2)
-    T = proj.shape[0]
-    if proj.shape[1] != heads * (nope + rot) + rank + rot:
-        raise KernelError(f"proj has {proj.shape[1]} columns, expected {heads * (nope + rot) + rank + rot}")
     nrot = 2 * cos.shape[1]
     if cos.shape != sin.shape or cos.shape[0] != T or nrot > rot:
         raise KernelError(f"cos/sin tables {tuple(cos.shape)} do not fit {T} tokens and {rot} rotated values")
-    if norm_weight.numel() != rank:
-        raise KernelError(f"norm weight has {norm_weight.numel()} entries for rank {rank}")
-    if write_cache:
-        _check(pages, "pages", proj.dtype, 4)
+    write = bool(write_cache) and latent is not None
+    if latent is not None:
+        _check(norm_weight, "norm_weight", torch.float32, 1)
+        if norm_weight.numel() != rank:
+            raise KernelError(f"norm weight has {norm_weight.numel()} entries for rank {rank}")
+    if write:
+        _check(pages, "pages", like.dtype, 4)
         if tuple(pages.shape[1:]) != (1, page_size, rank + rot):
             raise KernelError(f"pages have shape {tuple(pages.shape)}, expected [pages, 1, {page_size}, {rank + rot}]")
+    q_rank = 0
+    if query_latent is not None:
+        q_rank = query_latent.shape[1]
+        _check(query_norm_weight, "query_norm_weight", torch.float32, 1)
+        if query_norm_weight.numel() != q_rank:
+            raise KernelError(f"query norm weight has {query_norm_weight.numel()} entries for rank {q_rank}")
     f = _fn("latent_attention", "hb_latent_prepare",
-            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
-    _run(f(_p(proj), proj.shape[1], _p(pages) if write_cache else 0, _p(norm_weight), _p(cos), _p(sin),
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_int, c_int, c_void_p])
+    _run(f(_p(q), 0 if q is None else q.stride(0), _p(latent), 0 if latent is None else latent.stride(0),
+           _p(query_latent), 0 if query_latent is None else query_latent.stride(0), q_rank,
+           _p(query_norm_weight) if query_latent is not None else 0, _p(pages) if write else 0,
+           _p(norm_weight) if latent is not None else 0, _p(cos), _p(sin),
            _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1], T, heads, nope, rot,
-           rank, nrot, page_size, float(eps), 1 if write_cache else 0, _dt(proj.dtype), _stream()),
-         "latent_prepare")
+           rank, nrot, ROTARY_PAIRINGS[pairing], page_size, float(eps), 1 if write else 0, _dt(like.dtype),
+           _stream()), "latent_prepare")
 
 
 #: from this many tokens on the per-head products of a bfloat16 step go to the library's
@@ -1909,13 +1969,19 @@ ROUTER_KINDS = {"sigmoid": 0, "softmax": 1, "top_softmax": 2}
 
 
 def moe_topk(logits: torch.Tensor, top: int, kind: str = "sigmoid",
-             correction: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None):
+             correction: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+             groups=None, normalize: bool = False, scale: float = 1.0):
     """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router ``logits``
     [T, outputs] (+ ``bias``, float32 [outputs], added first).  Kinds "sigmoid" and "softmax":
     scores s = sigmoid(z), or softmax(z) over all outputs; the ``top`` largest s + correction
     (float32 [outputs]; None: s alone) are chosen, lower index on a tie, largest first; the
     weight is s itself.  Kind "top_softmax": the ``top`` largest logits are chosen and the
-    weights are the softmax over the chosen logits alone."""
+    weights are the softmax over the chosen logits alone.
+
+    ``groups`` = (count, keep): the router outputs form ``count`` equal runs of neighbours; a
+    run scores its largest choice value, and only outputs of the ``keep`` best runs (the lower
+    index among equals) can be chosen (rows of at most 256 outputs).  ``normalize``: the weights
+    are the chosen scores divided by their sum (+ 1e-20).  ``scale`` multiplies every weight."""
     _check(logits, "logits", torch.float32, 2)
     T, E = logits.shape
     if kind not in ROUTER_KINDS:
@@ -1927,13 +1993,19 @@ def moe_topk(logits: torch.Tensor, top: int, kind: str = "sigmoid",
             _check(v, name, torch.float32, 1)
             if v.numel() != E:
                 raise KernelError(f"{name} has {v.numel()} entries for {E} router outputs")
+    count, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+    if count > 1 and (E % count or not 0 < keep <= count or top > keep * (E // count) or E > 256):
+        raise KernelError(f"{count} groups of which {keep} stay do not fit top {top} of {E} router outputs "
+                          "(equal groups, at most 256 outputs)")
+    if normalize and kind == "top_softmax":
+        raise KernelError("a softmax over the chosen logits is normalised already")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     biased = torch.empty_like(logits) if bias is not None and E > 256 else None
     f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                   c_int, c_int, c_void_p])
+                                   c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _run(f(_p(ids), _p(weights), _p(logits), _p(correction), _p(bias), _p(biased), T, E, top,
-           ROUTER_KINDS[kind], _stream()), "moe_topk")
+           ROUTER_KINDS[kind], count, keep, 1 if normalize else 0, float(scale), _stream()), "moe_topk")
     return ids, weights
 
 

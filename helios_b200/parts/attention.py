@@ -140,9 +140,13 @@ class SinkGQAAttention(Mixer):
     ``values="keys"``     there is no W_v: v_j = W_k h_j (+ bias) as projected, before any
                           rotation or norm of the key
     ``qk_norm="plain"``   q and k are divided by their root mean square without a weight
+    ``qk_norm="row"``     the RMS norm runs over the WHOLE query projection and the whole key
+                          projection (all heads at once, weights of those sizes), and BEFORE the
+                          rotation
     ``position``, ``rotary_dim``  q and k are rotated BEFORE their norm by the tables of this
                           encoding, on the first ``rotary_dim`` values of a head, value i paired
-                          with value i + rotary_dim / 2
+                          with value i + rotary_dim / 2 (``rotary_pairing="halves"``) or value 2i
+                          with value 2i + 1 ("neighbours")
     ``distance_table``    (rows, far): a learned bias ``rel`` [rows, heads] by the distance i - j,
                           looked up through ``ops.distance_bias_rows``
     ``sink="learned"``    the sink's score is a learned number a head (tensor ``sink``) instead of 0
@@ -159,7 +163,7 @@ class SinkGQAAttention(Mixer):
                  names=("q", "k", "v", "o", "g", "q.norm", "k.norm"), values: str = "projected",
                  position=None, rotary_dim: int = 0, distance_table=None, keep_first: int = 0,
                  qk_bias: bool = False, out_bias: bool = False, rel_name: str = "rel",
-                 sink_name: str = "sink", bias_suffix: str = ".b") -> None:
+                 sink_name: str = "sink", bias_suffix: str = ".b", rotary_pairing: str = "halves") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
         value_dim = value_dim or head_dim
@@ -167,9 +171,11 @@ class SinkGQAAttention(Mixer):
             raise ValueError(f"heads of {head_dim} / {value_dim} values are not supported (at most 256)")
         if slopes is not None and len(slopes) != num_heads:
             raise ValueError(f"{len(slopes)} slopes for {num_heads} heads")
-        if values not in ("projected", "keys") or qk_norm not in (True, False, "plain") \
-                or sink not in (True, False, "learned") or head_gate not in (True, False, "wide"):
-            raise ValueError(f"values {values!r} / qk_norm {qk_norm!r} / sink {sink!r} / head_gate {head_gate!r}")
+        if values not in ("projected", "keys") or qk_norm not in (True, False, "plain", "row") \
+                or sink not in (True, False, "learned") or head_gate not in (True, False, "wide") \
+                or rotary_pairing not in ops.ROTARY_PAIRINGS:
+            raise ValueError(f"values {values!r} / qk_norm {qk_norm!r} / sink {sink!r} / head_gate {head_gate!r} "
+                             f"/ rotary_pairing {rotary_pairing!r}")
         if values == "keys" and value_dim != head_dim:
             raise ValueError("values that are the keys have the keys' size")
         if (position is None) != (not rotary_dim) or rotary_dim % 2 or rotary_dim > head_dim:
@@ -185,6 +191,7 @@ class SinkGQAAttention(Mixer):
         self.window = window
         self.names = tuple(names)
         self.values, self.position, self.rotary_dim = values, position, int(rotary_dim)
+        self.rotary_pairing = rotary_pairing
         self.distance_table = None if distance_table is None else (int(distance_table[0]), float(distance_table[1]))
         self.keep_first = int(keep_first or 0)
         self.qk_bias, self.out_bias = bool(qk_bias), bool(out_bias)
@@ -196,7 +203,7 @@ class SinkGQAAttention(Mixer):
         self._gate_col = q + kv + (num_kv_heads * value_dim if values == "projected" else 0)
         # the launch that readies q, k and v: the one with weights and temperature, or the one
         # that also rotates, norms without weights and may take the values from the keys
-        self._rotate_prepare = values == "keys" or position is not None or qk_norm == "plain"
+        self._rotate_prepare = values == "keys" or position is not None or qk_norm in ("plain", "row")
         if self._rotate_prepare and self.q_temperature is not None:
             raise ValueError("a query temperature goes with weighted q/k norms and projected values only")
         self._tiled_options = value_dim == head_dim
@@ -226,6 +233,9 @@ class SinkGQAAttention(Mixer):
         if self.qk_norm is True:
             specs[nqn] = WeightSpec((self.head_dim,), kind="vector", init="ones_jitter")
             specs[nkn] = WeightSpec((self.head_dim,), kind="vector", init="ones_jitter")
+        elif self.qk_norm == "row":
+            specs[nqn] = WeightSpec((q,), kind="vector", init="ones_jitter")
+            specs[nkn] = WeightSpec((kv,), kind="vector", init="ones_jitter")
         if self.qk_bias:
             for n in (nq, nk) + ((nv,) if self.values == "projected" else ()):
                 specs[n + self.bias_suffix] = WeightSpec((specs[n].shape[0],), kind="vector", init="normal")
@@ -257,7 +267,7 @@ class SinkGQAAttention(Mixer):
             self.b_in = torch.cat(biases).contiguous()
         if self.out_bias:
             self.b_o = tensors[no + self.bias_suffix].contiguous()
-        if self.qk_norm is True:
+        if self.qk_norm in (True, "row"):
             self.q_weight, self.k_weight = tensors[nqn].contiguous(), tensors[nkn].contiguous()
         if self.slope_values is not None:
             self.slopes = torch.tensor(self.slope_values, dtype=torch.float32, device=self.w_o.device)
@@ -284,8 +294,9 @@ class SinkGQAAttention(Mixer):
             gate = rows[:, self._gate_col:self._gate_col + n]
         if self._rotate_prepare:
             cos, sin = self.position.tables(ctx) if self.position is not None else (None, None)
-            prepare = ops.RotateNormPrepare(cos, sin, bool(self.qk_norm), self.q_weight, self.k_weight, self.eps,
-                                            self._value_col, cache.write)
+            prepare = ops.RotateNormPrepare(cos, sin, "row" if self.qk_norm == "row" else bool(self.qk_norm),
+                                            self.q_weight, self.k_weight, self.eps, self._value_col,
+                                            cache.write, pairing=self.rotary_pairing)
         else:
             coef, every = self.q_temperature or (0.0, 0)
             prepare = (self.q_weight, self.k_weight, self.eps, coef, every, cache.write)

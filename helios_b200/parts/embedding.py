@@ -10,10 +10,11 @@ from .base import InputStage, Norm, OutputStage, Part, PositionEncoding, WeightS
 
 
 class TokenEmbedding(InputStage):
-    """hidden = table[token ids]; no scale and no position term.  The residual stream
-    it starts is float32."""
+    """hidden = table[token ids] * scale (``scale`` 1: none); no position term.  The residual
+    stream it starts is float32, and so is the product."""
 
-    def __init__(self, vocab: int, width: int, tensor_name: str = "weight") -> None:
+    def __init__(self, vocab: int, width: int, tensor_name: str = "weight", scale: float = 1.0) -> None:
+        self.scale = float(scale)
         self.vocab = vocab
         self.vocab_size = vocab
         self.width = width
@@ -27,7 +28,7 @@ class TokenEmbedding(InputStage):
         self.table = tensors[self.tensor_name].contiguous()
 
     def forward(self, ctx) -> torch.Tensor:
-        return ops.embedding(ctx.token_ids, self.table)
+        return ops.embedding(ctx.token_ids, self.table, self.scale)
 
 
 class OutputHead(Part):

@@ -23,6 +23,10 @@ Options, each a constructor parameter with the form above as its default:
 ``identity``    this many router outputs beyond the experts stand for experts without
                 tensors whose output is their input
 ``shared_inner`` an expert of this inner size (same form) that every token runs, added to the sum
+``groups``      (count, keep): the experts form ``count`` equal groups of neighbours; a group scores
+                its best expert, and only experts of the ``keep`` best groups can be chosen
+``normalize``   the weights are the chosen scores divided by their sum (+ 1e-20)
+``weight_scale`` a constant on every weight
 """
 from __future__ import annotations
 
@@ -41,7 +45,8 @@ class RoutedExperts(FeedForward):
                  weight_on: str = "input", activation: str = "clamped_swish", identity: int = 0,
                  shared_inner: Optional[int] = None, correction_name: str = "correction",
                  shared_prefix: str = "shared.", router_bias: bool = False,
-                 router_bias_name: str = "router.b") -> None:
+                 router_bias_name: str = "router.b", groups=None, normalize: bool = False,
+                 weight_scale: float = 1.0) -> None:
         if not 0 < top <= experts + identity:
             raise ValueError(f"top {top} of {experts} + {identity} experts")
         if router not in ops.ROUTER_KINDS or weight_on not in ("input", "output") \
@@ -49,6 +54,14 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"router {router!r} / weight_on {weight_on!r} / activation {activation!r}")
         if identity and weight_on != "output":
             raise ValueError("experts without tensors need the weight on the output")
+        self.groups = None
+        if groups and int(groups[0]) > 1:
+            count, keep = int(groups[0]), int(groups[1])
+            if (experts + identity) % count or not 0 < keep <= count or top > keep * ((experts + identity) // count):
+                raise ValueError(f"{count} groups of which {keep} stay do not fit top {top} of "
+                                 f"{experts + identity} router outputs")
+            self.groups = (count, keep)
+        self.normalize, self.weight_scale = bool(normalize), float(weight_scale)
         self.width, self.inner, self.experts, self.top = width, inner, experts, top
         self.limit = float(limit)
         self.router_name, self.expert_prefix, self.names = router_name, expert_prefix, tuple(names)
@@ -107,7 +120,8 @@ class RoutedExperts(FeedForward):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear_logits(x, self.w_router)          # float32 [T, router outputs]
-        ids, weights = ops.moe_topk(logits, self.top, self.router, self.correction, self.router_bias)
+        ids, weights = ops.moe_topk(logits, self.top, self.router, self.correction, self.router_bias,
+                                    groups=self.groups, normalize=self.normalize, scale=self.weight_scale)
         base = None
         if self.shared_inner:
             if not self.gated:
