@@ -371,6 +371,48 @@ def gebasun_configs(size):
     return gb, mz
 
 
+def fobanex_configs(size):
+    """(Fobanex config.json, Mizerax config.json of equal width, heads, KV heads, layers,
+    vocabulary, experts and expert size) at layer sizes of a real model.  Six layers: attention
+    with the norm over the whole q and k projections, attention over a latent with a query
+    latent, the same on the rows of the layer before, attention whose values are its keys,
+    attention, latent attention; the first feed-forward dense, the others routed with the choice
+    among the best half of eight groups.  The Mizerax model beside it is the package's closest:
+    parallel blocks with one norm, attention with q/k norms and a gate, a routed feed-forward
+    with a softmax router and the weights on the outputs (no shared expert, no loop)."""
+    if size == "large":
+        width, heads, kv, hd, rank, experts, top, eff, vocab = 2048, 16, 4, 128, 512, 32, 4, 2048, 32000
+    else:
+        width, heads, kv, hd, rank, experts, top, eff, vocab = 1024, 8, 2, 64, 256, 16, 2, 2048, 32000
+    yarn = {"factor": 8.0, "fast": 32.0, "slow": 1.0, "original": 4096}
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 8, "keep": 4}}}
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                     "rot": {"dims": hd // 2, "base": 1000000.0, "scaling": yarn}}}
+    att2 = {"type": "attention_2",
+            "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                      "rot": {"dims": hd // 2, "base": 10000.0, "scaling": yarn}}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": rank,
+                     "q_rank": 3 * rank // 2, "scale": (hd + hd // 2) ** -0.5, "rot": {"dims": hd // 2, "base": 10000.0}}}
+    layers = []
+    for i, kind in enumerate(("A", "L", "B", "K", "A", "L")):
+        layer = json.loads(json.dumps({"A": att, "K": att2}.get(kind, lat)))
+        if kind == "B":
+            layer["mixer"]["kv_from"] = i - 1
+        layer["mlp"] = {"kind": "dense", "ff": top * eff} if i == 0 else moe
+        layers.append(layer)
+    fb = {"architecture": "Fobanex", "vocab": vocab, "width": width, "embedding": {"scale": float(width) ** 0.5},
+          "norm": {"eps": 1e-5}, "layers": layers}
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5},
+             "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top}}}
+    mz = {"architecture": "Mizerax", "vocab": vocab, "width": width, "max_positions": 8192,
+          "norm": {"eps": 1e-5}, "layers": [dict(layer) for _ in range(6)]}
+    return fb, mz
+
+
 def design_configs(size, design="zokelix"):
     """(Zokelix config.json, dense decoder config.json of equal width, head count, layers, vocabulary
     and active feed-forward size) at layer sizes of a real model.  Six layers: attention over a
@@ -380,6 +422,8 @@ def design_configs(size, design="zokelix"):
         return mizerax_configs(size)
     if design == "gebasun":
         return gebasun_configs(size)
+    if design == "fobanex":
+        return fobanex_configs(size)
     if size == "large":
         width, heads, hd, rank, ff, experts, top, eff, vocab = 2048, 16, 128, 512, 8192, 32, 4, 2048, 32000
     else:
@@ -439,7 +483,8 @@ def run_design(args):
            "embedding", "rotary_table", "attention", "latent_prepare", "head_gemm", "latent_attention",
            "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts",
            "add_layernorm", "qk_norm_kv_write", "add_table_rows", "cast_rows",
-           "add_rmsnorm_pair", "qk_rotate_norm_write", "ssm_scan", "gated_group_rmsnorm", "unary_act", "sigmoid_gate"]
+           "add_rmsnorm_pair", "qk_rotate_norm_write", "ssm_scan", "gated_group_rmsnorm", "unary_act", "sigmoid_gate",
+           "latent_prepare_parts", "linear_rows"]
 
     def op_table(core, entries_fn, reps=3):
         """milliseconds per op name over one step, run kernel by kernel (nested ops count inside
@@ -482,7 +527,7 @@ def run_design(args):
     for size in [s for s in args.design_sizes.split(",") if s]:
         zk, dense = design_configs(size, args.design)
         res = {}
-        for label, cfg in ((args.design, zk), ("mizerax" if args.design == "gebasun" else "dense", dense)):
+        for label, cfg in ((args.design, zk), ("mizerax" if args.design in ("gebasun", "fobanex") else "dense", dense)):
             vocab = cfg.get("vocab") or cfg["vocab_size"]
             model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
             batches = [int(b) for b in args.design_batches.split(",")]
@@ -739,7 +784,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--design", default=None, choices=["zokelix", "mizerax", "gebasun"],
+    ap.add_argument("--design", default=None, choices=["zokelix", "mizerax", "gebasun", "fobanex"],
                     help="measure another design of the package beside a dense decoder of equal size "
                          "(prefill, decode, time by op) instead of the default workload")
     ap.add_argument("--design-sizes", default="small,large")

@@ -1255,3 +1255,73 @@ HB_EXPORT int hb_unary_act(void* out, const void* x, const void* gate, int gate_
               (const TA*)gate, gate_ld, total, W, kind));
   return hb_check_launch();
 }
+
+// ---------------------------------------------------------------- a gate on every value of every head
+// out[t, h * N + n] = x[t, h, n] * sigmoid(gate[t, h * N + n]): x is a view [T, H, N] with a
+// token stride and a head stride (what a batched product of one matrix a head leaves), gate rows
+// are gate_ld apart, out is contiguous.  float32 arithmetic.
+template <typename T>
+__global__ void gate_heads_kernel(T* __restrict__ out, const T* __restrict__ x, long x_token, long x_head,
+                                  const T* __restrict__ gate, int gate_ld, size_t total, int H, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W = H * N;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / W;
+    const int c = (int)(idx - t * W), h = c / N, n = c - h * N;
+    const float v = to_float(x[t * x_token + (size_t)h * x_head + n]);
+    const float g = to_float(gate[t * (size_t)gate_ld + c]);
+    out[idx] = from_float<T>(v / (1.f + expf(-g)));
+  }
+}
+
+// bfloat16, N a multiple of 8 and every row 16-byte aligned: eight values a thread and step
+__global__ void gate_heads_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                                         long x_token, long x_head, const __nv_bfloat16* __restrict__ gate,
+                                         int gate_ld, size_t pieces, int H, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int W8 = H * N / 8, N8 = N / 8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < pieces;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / W8;
+    const int c = (int)(idx - t * W8), h = c / N8, n = (c - h * N8) * 8;
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + t * x_token + (size_t)h * x_head + n);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate + t * (size_t)gate_ld + (size_t)c * 8);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    uint4 ov;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = __bfloat1622float2(xp[i]), g = __bfloat1622float2(gp[i]);
+      op[i] = __floats2bfloat162_rn(a.x / (1.f + expf(-g.x)), a.y / (1.f + expf(-g.y)));
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = ov;
+  }
+}
+
+HB_EXPORT int hb_gate_heads(void* out, const void* x, long x_token, long x_head, const void* gate, int gate_ld,
+                            int T, int H, int N, int act_dt, cudaStream_t stream) {
+  if (T <= 0 || H <= 0 || N <= 0) return HB_OK;
+  if (gate == nullptr || gate_ld < H * N) return HB_BAD_ARGUMENT;
+  const size_t total = (size_t)T * H * N;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
+                         reinterpret_cast<uintptr_t>(gate)) & 15) == 0;
+  if (act_dt == HB_BF16 && N % 8 == 0 && x_token % 8 == 0 && x_head % 8 == 0 && gate_ld % 8 == 0 && aligned) {
+    const size_t pieces = total / 8;
+    size_t blocks = (pieces + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    hb_launch(gate_heads_bf16x8_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
+              (const __nv_bfloat16*)x, x_token, x_head, (const __nv_bfloat16*)gate, gate_ld, pieces, H, N);
+    return hb_check_launch();
+  }
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(gate_heads_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out, (const TA*)x,
+              x_token, x_head, (const TA*)gate, gate_ld, total, H, N));
+  return hb_check_launch();
+}
+

@@ -237,6 +237,25 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gate_heads(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """out[t, h * N + n] = x[t, h, n] * sigmoid(gate[t, h * N + n]): ``x`` is a view [T, H, N]
+    whose last dimension is contiguous (the result of one small product a head, whatever its
+    token and head strides: no copy is made), ``gate`` [T, >= H * N] a view whose rows may be
+    strided.  Returns a contiguous [T, H * N]."""
+    if x.dim() != 3 or x.stride(2) != 1 or not x.is_cuda:
+        raise KernelError(f"gate_heads: x {tuple(x.shape)} must be [T, H, N] with a contiguous last dimension")
+    T, H, N = x.shape
+    if gate.dim() != 2 or gate.stride(1) != 1 or gate.dtype != x.dtype or gate.shape[0] != T \
+            or gate.shape[1] < H * N or not gate.is_cuda:
+        raise KernelError(f"gate {tuple(gate.shape)} does not fit x {tuple(x.shape)}")
+    out = torch.empty((T, H * N), dtype=x.dtype, device=x.device)
+    f = _fn("elementwise", "hb_gate_heads", [c_void_p, c_void_p, ctypes.c_long, ctypes.c_long, c_void_p, c_int,
+                                             c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), x.stride(0), x.stride(1), _p(gate), gate.stride(0), T, H, N, _dt(x.dtype), _stream()),
+         "gate_heads")
+    return out
+
+
 def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float = 1.0):
     """cos and sin [T, rot/2] (float32) of position * inv_freq, computed in float64 and
     multiplied by ``factor`` (the attention factor of a scaled encoding; 1 for none)."""

@@ -139,9 +139,11 @@ class LatentAttention(Mixer):
         q_lat = ops.head_gemm(q[:, :, :self.nope], self.w_uk_t)
         o_lat = ops.latent_attention(ctx, q_lat, q[:, :, self.nope:], cache.k_pages, table,
                                      self.rank, self.rot, cache.page_size, self.scale)
-        o = ops.head_gemm(o_lat, self.w_uv).reshape(T, H * self.vdim)
-        if self.gate:
-            o = ops.sigmoid_gate(o, proj[:, self._gate_col:self._gate_col + H * self.vdim])
+        o = ops.head_gemm(o_lat, self.w_uv)
+        if self.gate:          # the gate's launch also lays the heads side by side, whatever the product's strides
+            o = ops.gate_heads(o, proj[:, self._gate_col:self._gate_col + H * self.vdim])
+        else:
+            o = o.reshape(T, H * self.vdim)
         return ops.linear(o, self.w_o)
 
 

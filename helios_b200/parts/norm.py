@@ -30,9 +30,17 @@ class RMSNorm(Norm):
 
     def add_forward(self, residual, delta, out_dtype, rows=None):
         if isinstance(delta, PendingSum):
+            # what a block with ONE norm left pending (plain terms) rides in the norm's own launch
+            if rows is None and self._plain(delta):
+                (a, _), (b, _) = (delta.terms + [(None, None)] * 2)[:2]
+                return ops.add_rmsnorm_pair(residual, a, b, self.weight, None, self.eps, out_dtype)[0]
             settle(residual, delta)
             delta = None
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype, rows)
+
+    @staticmethod
+    def _plain(delta: PendingSum) -> bool:
+        return delta.mult == 1.0 and len(delta.terms) <= 2 and all(s is None for _t, s in delta.terms)
 
     def add_forward_pair(self, residual, delta, other: "Norm", out_dtype):
         """``residual += delta`` (a tensor, a ``PendingSum`` or None), then this norm AND
@@ -40,8 +48,7 @@ class RMSNorm(Norm):
         eps share the row's 1 / rms, and a pending sum of plain terms rides along: one kernel."""
         if type(other) is RMSNorm and other.eps == self.eps and other.width == self.width:
             if isinstance(delta, PendingSum):
-                plain = delta.mult == 1.0 and len(delta.terms) <= 2 and all(s is None for _t, s in delta.terms)
-                if plain:
+                if self._plain(delta):
                     (a, _), (b, _) = (delta.terms + [(None, None)] * 2)[:2]
                     return ops.add_rmsnorm_pair(residual, a, b, self.weight, other.weight, self.eps, out_dtype)
                 settle(residual, delta)

@@ -450,6 +450,25 @@ def test_query_latent_norm_latent_rows_and_rotation_of_halves(dtype, heads, nope
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype,T,H,N", [("float32", 5, 3, 6), ("bfloat16", 40, 4, 32), ("bfloat16", 3, 2, 12),
+                                         ("float32", 70, 6, 16)])
+def test_gate_on_every_value_of_heads_that_lie_apart(dtype, T, H, N):
+    """The heads' outputs as a batched product leaves them (head-major) and as rows; the gate a
+    column slice of wider rows."""
+    from helios_b200.csrc import ops
+
+    dt = _dt(dtype)
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(H, T, N, generator=g).to(dt)
+    wide = (3 * torch.randn(T, H * N + 16, generator=g)).to(dt)
+    want = x.double().transpose(0, 1).reshape(T, H * N) * torch.sigmoid(wide.double()[:, 8:8 + H * N])
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    for view in (x.cuda().transpose(0, 1), x.transpose(0, 1).contiguous().cuda()):
+        got = ops.gate_heads(view, wide.cuda()[:, 8:8 + H * N])
+        assert got.is_contiguous() and (got.float().cpu().double() - want).abs().max() < tol * float(want.abs().max())
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("experts,top,groups,scale", [(12, 4, (3, 2), 1.5), (8, 2, (4, 2), 1.0), (6, 3, None, 2.0),
                                                       (6, 1, (3, 1), 1.0), (6, 2, (6, 6), 0.5), (7, 7, (1, 1), 1.0),
                                                       (64, 8, (8, 3), 2.5), (256, 6, (32, 4), 1.0), (40, 3, (20, 2), 1.0)])
