@@ -1152,6 +1152,117 @@ qk_rownorm_rotate_write_kernel(T* __restrict__ rows, int ld, int v_col, const fl
                 page_size, write_cache, t, h, head_sm[warp], lane, h < nh ? fq : fk);
 }
 
+// The same with 16-byte pieces, for rows whose heads, strides and offsets are whole pieces (8
+// bfloat16 or 4 float32 values): the q and k rows pass through shared memory as floats once;
+// the sums of squares are taken while they are loaded (a thread's pieces in their order, then
+// the block's fixed tree); after ONE barrier every thread norms, weights and rotates pieces
+// (a neighbour pair lies inside a piece; the partner of a halves pair is read from shared
+// memory with its own weight) and stores them whole; value heads are copied piece by piece.
+constexpr int QKR_FAST_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(QKR_FAST_THREADS)
+qk_rownorm_rotate_write_vec_kernel(T* __restrict__ rows, int ld, int v_col, const float* __restrict__ cos_tab,
+                                   const float* __restrict__ sin_tab, int rot, int pairing,
+                                   const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
+                                   T* __restrict__ v_pages, int nh, int nkv, int hd, int vd,
+                                   const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                   int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ float qkr_sm[];            // [nq + nk] the rows as floats, then 66 floats of scratch
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int nq = nh * hd, nk = nkv * hd, n = nq + nk;
+  float* scratch = qkr_sm + n;
+  T* row = rows + (size_t)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int c = tid * V; c < n; c += QKR_FAST_THREADS * V) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+    const T* e = reinterpret_cast<const T*>(&raw);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float v = to_float(e[i]); qkr_sm[c + i] = v; part = fmaf(v, v, part); }
+    if (c < nq) sq += part; else sk += part;
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if ((tid & 31) == 0) { scratch[tid >> 5] = sq; scratch[32 + (tid >> 5)] = sk; }
+  __syncthreads();
+  float tq = 0.f, tk = 0.f;
+#pragma unroll
+  for (int w = 0; w < QKR_FAST_THREADS / 32; ++w) { tq += scratch[w]; tk += scratch[32 + w]; }
+  const float fq = rsqrtf(tq / (float)nq + eps), fk = rsqrtf(tk / (float)nk + eps);
+  const int pos = positions[t];
+  size_t page_base = 0;
+  int slot = 0;
+  if (write_cache) {
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    slot = pos % page_size;
+    page_base = (size_t)page * nkv;
+  }
+  const int half = rot >> 1;
+  const float* cr = cos_tab ? cos_tab + (size_t)t * half : nullptr;
+  const float* sr = sin_tab ? sin_tab + (size_t)t * half : nullptr;
+  for (int c = tid * V; c < n; c += QKR_FAST_THREADS * V) {
+    const bool is_q = c < nq;
+    const int cc = is_q ? c : c - nq;                 // column inside the q or the k row
+    const int h = cc / hd, d0 = cc - h * hd;
+    const float f = is_q ? fq : fk;
+    const float* w = is_q ? wq : wk;
+    const float* x = qkr_sm + c;
+    float y[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) y[i] = x[i] * f * (w ? w[cc + i] : 1.f);
+    if (!is_q && write_cache && v_col < 0) {          // the values are the keys as projected
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int i = 0; i < V; ++i) o[i] = from_float<T>(x[i]);
+      *reinterpret_cast<uint4*>(v_pages + ((page_base + h) * page_size + slot) * vd + d0) = out;
+    }
+    if (d0 < rot) {
+      if (pairing == QKR_NEIGHBOURS) {
+#pragma unroll
+        for (int i = 0; i < V; i += 2) {
+          if (d0 + i < rot) {
+            const float co = cr[(d0 + i) >> 1], si = sr[(d0 + i) >> 1];
+            const float u = y[i], v = y[i + 1];
+            y[i] = u * co - v * si;
+            y[i + 1] = v * co + u * si;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const int d = d0 + i;
+          if (d < rot) {
+            const bool low = d < half;
+            const int j = low ? d : d - half, pd = low ? d + half : d - half;
+            const float partner = qkr_sm[c - d0 + pd] * f * (w ? w[cc - d0 + pd] : 1.f);
+            y[i] = low ? y[i] * cr[j] - partner * sr[j] : y[i] * cr[j] + partner * sr[j];
+          }
+        }
+      }
+    }
+    uint4 out;
+    T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+    for (int i = 0; i < V; ++i) o[i] = from_float<T>(y[i]);
+    T* dst = (!is_q && write_cache) ? k_pages + ((page_base + h) * page_size + slot) * hd + d0 : row + c;
+    *reinterpret_cast<uint4*>(dst) = out;
+  }
+  if (write_cache && v_col >= 0) {
+    const int nv = nkv * vd;
+    for (int c = tid * V; c < nv; c += QKR_FAST_THREADS * V) {
+      const int g = c / vd, d0 = c - g * vd;
+      *reinterpret_cast<uint4*>(v_pages + ((page_base + g) * page_size + slot) * vd + d0) =
+          *reinterpret_cast<const uint4*>(row + v_col + c);
+    }
+  }
+}
+
 HB_EXPORT int hb_qk_rotate_norm_write(void* rows, int ld, int v_col, const float* cos_tab,
                                       const float* sin_tab, int rot, int pairing, const int* positions,
                                       const int* seq_of_token, const int* block_table, int bt_stride,
@@ -1165,6 +1276,23 @@ HB_EXPORT int hb_qk_rotate_norm_write(void* rows, int ld, int v_col, const float
       (v_col < 0 && vd != hd) || (long)(nh + nkv) * hd > ld || (v_col >= 0 && (long)v_col + (long)nkv * vd > ld))
     return HB_BAD_ARGUMENT;
   if (norm == QKR_NORM_ROW) {
+    // 16-byte pieces where every head, stride and offset is a whole number of them
+    const int V = act_dt == HB_BF16 ? 8 : 4;
+    const size_t smem = ((size_t)(nh + nkv) * hd + 66) * sizeof(float);
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(k_pages) |
+                           reinterpret_cast<uintptr_t>(v_pages);
+    if (hd % V == 0 && vd % V == 0 && ld % V == 0 && (v_col < 0 || v_col % V == 0) && (bits & 15) == 0 &&
+        smem <= 200 * 1024) {
+      HB_DISPATCH_DTYPE(act_dt, TA, {
+        if (smem > 48 * 1024)
+          cudaFuncSetAttribute(qk_rownorm_rotate_write_vec_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem);
+        hb_launch(qk_rownorm_rotate_write_vec_kernel<TA>, dim3((unsigned)T), dim3(QKR_FAST_THREADS), smem, stream,
+                  (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, pairing, positions, seq_of_token, block_table,
+                  bt_stride, (TA*)k_pages, (TA*)v_pages, nh, nkv, hd, vd, wq, wk, eps, page_size, write_cache);
+      });
+      return hb_check_launch();
+    }
     HB_DISPATCH_DTYPE(act_dt, TA,
       hb_launch(qk_rownorm_rotate_write_kernel<TA>, dim3((unsigned)T), dim3(QKR_ROW_WARPS * 32), 0, stream,
                 (TA*)rows, ld, v_col, cos_tab, sin_tab, rot, pairing, positions, seq_of_token, block_table,

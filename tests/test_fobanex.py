@@ -341,13 +341,18 @@ def test_embedding_times_a_constant(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype,nh,nkv,hd,vd,rot,own_values", [
-    ("float32", 4, 2, 24, 24, 8, True), ("float32", 3, 3, 10, 14, 10, True), ("bfloat16", 4, 1, 64, 64, 16, True),
-    ("bfloat16", 6, 2, 96, 96, 96, True), ("float32", 5, 1, 40, 40, 0, True), ("bfloat16", 2, 2, 32, 32, 2, True),
-    ("float32", 4, 2, 16, 16, 6, False), ("bfloat16", 8, 4, 128, 128, 64, False)])
-def test_norm_over_whole_projections_neighbour_rotation_and_the_cache_write(dtype, nh, nkv, hd, vd, rot, own_values):
-    """q and k normed over all heads at once with weights of that size, THEN rotated in
-    neighbouring pairs on the first ``rot`` values of every head; k to the key pages, v (columns
+@pytest.mark.parametrize("pairing", ["neighbours", "halves"])
+@pytest.mark.parametrize("dtype,nh,nkv,hd,vd,rot,own_values,norm", [
+    ("float32", 4, 2, 24, 24, 8, True, True), ("float32", 3, 3, 10, 14, 10, True, True),
+    ("bfloat16", 4, 1, 64, 64, 16, True, True), ("bfloat16", 6, 2, 96, 96, 96, True, True),
+    ("float32", 5, 1, 40, 40, 0, True, True), ("bfloat16", 2, 2, 32, 32, 2, True, True),
+    ("bfloat16", 4, 2, 64, 40, 32, True, True), ("bfloat16", 3, 1, 20, 20, 6, True, True),
+    ("float32", 4, 2, 16, 16, 6, False, False), ("bfloat16", 8, 4, 128, 128, 64, False, False),
+    ("bfloat16", 4, 2, 32, 32, 8, False, True), ("float32", 2, 1, 12, 12, 12, False, True)])
+def test_norm_over_whole_projections_neighbour_rotation_and_the_cache_write(dtype, nh, nkv, hd, vd, rot, own_values,
+                                                                            norm, pairing):
+    """q and k normed over all heads at once with weights of that size, THEN rotated (in
+    neighbouring pairs, or value i with value i + rot / 2) on the first ``rot`` values of every head; k to the key pages, v (columns
     of its own, or the keys as projected) to the value pages; pages in a scrambled order."""
     from helios_b200.csrc import ops
 
@@ -363,7 +368,6 @@ def test_norm_over_whole_projections_neighbour_rotation_and_the_cache_write(dtyp
     table = torch.tensor([[5, 2, 9, 0, 7, 1], [3, 4, 6, 8, 10, 11]], dtype=torch.int32)
     kp = torch.full((12, nkv, page, hd), float("nan"), dtype=dt)
     vp = torch.full((12, nkv, page, vd), float("nan"), dtype=dt)
-    norm = own_values          # the form without a value projection has no norm either
     wq = (1.0 + 0.3 * torch.randn(nh * hd, generator=g)) if norm else None
     wk = (1.0 + 0.3 * torch.randn(nkv * hd, generator=g)) if norm else None
     rcfg = {"dims": rot, "base": base}
@@ -375,14 +379,15 @@ def test_norm_over_whole_projections_neighbour_rotation_and_the_cache_write(dtyp
     r, kpd, vpd = rows.cuda(), kp.cuda(), vp.cuda()
     ops.qk_rotate_norm_write(r, cos, sin, positions.cuda(), seq_of.cuda(), table.cuda(), kpd, vpd, nh, nkv, hd, vd,
                              page, "row" if norm else False, wq.cuda() if norm else None,
-                             wk.cuda() if norm else None, eps, v_col, write_cache=True, pairing="neighbours")
+                             wk.cuda() if norm else None, eps, v_col, write_cache=True, pairing=pairing)
+    rotate = pf.rotate_neighbours if pairing == "neighbours" else pf.rotate_halves
     x = rows.double()
     q, k = x[:, :nh * hd], x[:, nh * hd:(nh + nkv) * hd]
     if norm:
         q, k = pf.rms_norm(q, wq.double(), eps), pf.rms_norm(k, wk.double(), eps)
     q, k = q.reshape(T, nh, hd), k.reshape(T, nkv, hd)
     if rot:
-        q, k = pf.rotate_neighbours(q, positions, rcfg), pf.rotate_neighbours(k, positions, rcfg)
+        q, k = rotate(q, positions, rcfg), rotate(k, positions, rcfg)
     v = x[:, v_col:v_col + nkv * vd].reshape(T, nkv, vd) if own_values else x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
     tol = 2e-5 if dtype == "float32" else 2.5e-2
     got_q = r.float().cpu().double()[:, :nh * hd].reshape(T, nh, hd)
