@@ -484,7 +484,7 @@ def run_design(args):
            "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts",
            "add_layernorm", "qk_norm_kv_write", "add_table_rows", "cast_rows",
            "add_rmsnorm_pair", "qk_rotate_norm_write", "ssm_scan", "gated_group_rmsnorm", "unary_act", "sigmoid_gate",
-           "latent_prepare_parts", "linear_rows"]
+           "latent_prepare_parts", "linear_rows", "gate_heads"]
 
     def op_table(core, entries_fn, reps=3):
         """milliseconds per op name over one step, run kernel by kernel (nested ops count inside
