@@ -17,7 +17,8 @@
 // ---------------------------------------------------------------- prepare
 // What the rows of the projections want before attention; every piece is optional (a null
 // pointer leaves it out), one block a token:
-//   cq  [T, cq_ld]: a query latent of `q_rank` values, RMS-normed in place (weight cq_w);
+//   cq  [T, cq_ld]: a query latent of `q_rank` values, RMS-normed (weight cq_w) into cq_out
+//       [T, cq_out_ld] (which may be cq itself: in place);
 //   lat [T, lat_ld] = [latent (rank) | shared key part (rot)]: the latent RMS-normed (weight
 //       norm_w), the shared key part rotated, both stored as the token's row of `pages`
 //       (with `write_cache`; without it nothing of `lat` is used: another layer's rows serve);
@@ -41,7 +42,8 @@ __device__ __forceinline__ void latent_rotate(T* __restrict__ dst, const T* __re
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_prepare_kernel(T* __restrict__ q, int q_ld, const T* __restrict__ lat_rows, int lat_ld,
-                      T* __restrict__ cq, int cq_ld, int q_rank, const float* __restrict__ cq_w,
+                      const T* cq, int cq_ld, T* cq_out, int cq_out_ld, int q_rank,
+                      const float* __restrict__ cq_w,
                       T* __restrict__ pages, const float* __restrict__ norm_w,
                       const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -54,13 +56,14 @@ latent_prepare_kernel(T* __restrict__ q, int q_ld, const T* __restrict__ lat_row
   const int half = nrot / 2;
   const float* ct = cos_tab + (size_t)t * half;
   const float* st = sin_tab + (size_t)t * half;
-  if (cq) {                                  // the query latent, normed in float32 in place
-    T* row = cq + (size_t)t * cq_ld;
+  if (cq) {                                  // the query latent, normed in float32
+    const T* row = cq + (size_t)t * cq_ld;
+    T* out = cq_out + (size_t)t * cq_out_ld;
     float ss = 0.f;
     for (int c = threadIdx.x; c < q_rank; c += blockDim.x) { const float v = to_float(row[c]); ss += v * v; }
     const float rstd = rsqrtf(block_sum(ss, scratch) / (float)q_rank + eps);
     for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
-      row[c] = from_float<T>(to_float(row[c]) * rstd * cq_w[c]);
+      out[c] = from_float<T>(to_float(row[c]) * rstd * cq_w[c]);
   }
   if (lat_rows && write_cache) {
     const T* lat = lat_rows + (size_t)t * lat_ld;
@@ -88,8 +91,9 @@ latent_prepare_kernel(T* __restrict__ q, int q_ld, const T* __restrict__ lat_row
   }
 }
 
-HB_EXPORT int hb_latent_prepare(void* q, int q_ld, const void* lat, int lat_ld, void* cq, int cq_ld,
-                                int q_rank, const float* cq_w, void* pages, const float* norm_w,
+HB_EXPORT int hb_latent_prepare(void* q, int q_ld, const void* lat, int lat_ld, const void* cq, int cq_ld,
+                                void* cq_out, int cq_out_ld, int q_rank, const float* cq_w, void* pages,
+                                const float* norm_w,
                                 const float* cos_tab, const float* sin_tab, const int* positions,
                                 const int* seq_of_token, const int* block_table, int bt_stride,
                                 int T, int heads, int nope, int rot, int rank, int nrot, int pairing,
@@ -99,13 +103,13 @@ HB_EXPORT int hb_latent_prepare(void* q, int q_ld, const void* lat, int lat_ld, 
   if (heads <= 0 || nope < 0 || rot < 0 || rank <= 0 || nrot < 0 || nrot > rot || nrot % 2 ||
       page_size <= 0 || (pairing != LAT_HALVES && pairing != LAT_NEIGHBOURS) ||
       (q && q_ld < heads * (nope + rot)) || (lat && lat_ld < rank + rot) ||
-      (cq && (q_rank <= 0 || cq_ld < q_rank || cq_w == nullptr)) ||
+      (cq && (q_rank <= 0 || cq_ld < q_rank || cq_w == nullptr || cq_out == nullptr || cq_out_ld < q_rank)) ||
       (lat && write_cache && (pages == nullptr || norm_w == nullptr)) ||
       (nrot > 0 && (cos_tab == nullptr || sin_tab == nullptr)))
     return HB_BAD_ARGUMENT;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(latent_prepare_kernel<TA>, dim3(T), dim3(128), 0, stream, (TA*)q, q_ld, (const TA*)lat, lat_ld,
-              (TA*)cq, cq_ld, q_rank, cq_w, (TA*)pages, norm_w, cos_tab, sin_tab, positions, seq_of_token,
+              (const TA*)cq, cq_ld, (TA*)cq_out, cq_out_ld, q_rank, cq_w, (TA*)pages, norm_w, cos_tab, sin_tab, positions, seq_of_token,
               block_table, bt_stride, heads, nope, rot, rank, nrot, pairing, page_size, eps, write_cache));
   return hb_check_launch();
 }

@@ -1656,11 +1656,12 @@ def latent_prepare_parts(q: Optional[torch.Tensor], latent: Optional[torch.Tenso
                          cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
                          seq_of_token: torch.Tensor, block_table: torch.Tensor, heads: int, nope: int,
                          rot: int, rank: int, page_size: int, eps: float, write_cache: bool = True,
-                         pairing: str = "halves") -> None:
+                         pairing: str = "halves", query_latent_out: Optional[torch.Tensor] = None) -> None:
     """``latent_prepare`` piece by piece; each of the three tensors is a view [T, columns] whose
     rows may be strided (last dimension contiguous), or None to leave the piece out:
 
-    ``query_latent`` [T, q_rank]: RMS-normed in place (``query_norm_weight``);
+    ``query_latent`` [T, q_rank]: RMS-normed (``query_norm_weight``) in place, or into
+    ``query_latent_out`` (the same shape; contiguous rows suit the product that follows);
     ``latent`` [T, rank + rot] = [latent | shared key part]: the latent RMS-normed
     (``norm_weight``), the shared key part rotated, both stored as the token's row of ``pages``
     (nothing without ``write_cache``: the rows of another layer serve);
@@ -1674,8 +1675,12 @@ def latent_prepare_parts(q: Optional[torch.Tensor], latent: Optional[torch.Tenso
     if pairing not in ROTARY_PAIRINGS:
         raise KernelError(f"pairing {pairing!r} is not one of {sorted(ROTARY_PAIRINGS)}")
     T = like.shape[0]
+    if query_latent_out is None:
+        query_latent_out = query_latent
+    elif query_latent is None or query_latent_out.shape != query_latent.shape:
+        raise KernelError("latent_prepare: query_latent_out goes with a query_latent of its shape")
     for name, x, cols in (("q", q, heads * (nope + rot)), ("latent", latent, rank + rot),
-                          ("query_latent", query_latent, None)):
+                          ("query_latent", query_latent, None), ("query_latent_out", query_latent_out, None)):
         if x is None:
             continue
         if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.shape[0] != T or x.dtype != like.dtype \
@@ -1705,11 +1710,12 @@ def latent_prepare_parts(q: Optional[torch.Tensor], latent: Optional[torch.Tenso
         if query_norm_weight.numel() != q_rank:
             raise KernelError(f"query norm weight has {query_norm_weight.numel()} entries for rank {q_rank}")
     f = _fn("latent_attention", "hb_latent_prepare",
-            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_float, c_int, c_int, c_void_p])
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _run(f(_p(q), 0 if q is None else q.stride(0), _p(latent), 0 if latent is None else latent.stride(0),
-           _p(query_latent), 0 if query_latent is None else query_latent.stride(0), q_rank,
+           _p(query_latent), 0 if query_latent is None else query_latent.stride(0),
+           _p(query_latent_out), 0 if query_latent_out is None else query_latent_out.stride(0), q_rank,
            _p(query_norm_weight) if query_latent is not None else 0, _p(pages) if write else 0,
            _p(norm_weight) if latent is not None else 0, _p(cos), _p(sin),
            _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1], T, heads, nope, rot,

@@ -121,15 +121,19 @@ class LatentAttention(Mixer):
         first = proj[:, :self._n_first]
         latent = proj[:, self._lat_col:self._lat_col + self.rank + self.rot] if self.own_rows else None
 
-        def prepare(q, lat, query_latent):
+        def prepare(q, lat, query_latent, out=None):
             ops.latent_prepare_parts(q, lat, query_latent, cache.k_pages, self.norm_weight,
                                      self.query_norm_weight, cos, sin, ctx.positions, ctx.seq_of_token,
                                      table, H, self.nope, self.rot, self.rank, cache.page_size, self.eps,
-                                     write_cache=cache.write and self.own_rows, pairing=self.pairing)
+                                     write_cache=cache.write and self.own_rows, pairing=self.pairing,
+                                     query_latent_out=out)
 
         if self.q_rank:
-            prepare(None, latent, first)                     # the query latent normed, the rows stored
-            q = ops.linear_rows(first, self.w_uq)
+            # the query latent normed into rows of its own (the product that follows wants
+            # contiguous rows), the latent rows stored
+            cq = torch.empty((T, self.q_rank), dtype=proj.dtype, device=proj.device)
+            prepare(None, latent, first, cq)
+            q = ops.linear(cq, self.w_uq)
             prepare(q, None, None)
         else:
             q = first

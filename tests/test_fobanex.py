@@ -428,8 +428,13 @@ def test_query_latent_norm_latent_rows_and_rotation_of_halves(dtype, heads, nope
     pages = torch.full((12, 1, page, rank + rot), float("nan"), dtype=dt).cuda()
     fd, qd = first.cuda(), q.cuda()
     args = (cos, sin, positions.cuda(), seq_of.cuda(), table.cuda(), heads, nope, rot, rank, page, eps)
+    apart = torch.full((T, q_rank), float("nan"), dtype=dt).cuda()        # the normed query latent in rows of its own
+    ops.latent_prepare_parts(None, None, fd[:, :q_rank], None, None, wqn.cuda(), *args, pairing=pairing,
+                             query_latent_out=apart)
+    assert torch.equal(fd.cpu(), first)
     ops.latent_prepare_parts(None, fd[:, q_rank:q_rank + rank + rot], fd[:, :q_rank], pages, wn.cuda(), wqn.cuda(),
                              *args, write_cache=True, pairing=pairing)
+    assert torch.equal(apart, fd[:, :q_rank])
     ops.latent_prepare_parts(qd, None, None, None, None, None, *args, pairing=pairing)
     rotate = pf.rotate_halves if pairing == "halves" else pf.rotate_neighbours
     x = first.double()
